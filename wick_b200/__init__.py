@@ -13,8 +13,10 @@ generation loop, sampling, and hand-written CUDA kernels for sm_100a.
 """
 from .config.base import (ConfigError, ModelConfig, architecture_names, config_from_json, get_architecture,
                           load_config, register_architecture, Architecture)
+from .config.nibotar import NibotarConfig
 from .config.qwen3 import Qwen3Config
 from .models import qwen3 as _qwen3  # registers the architecture  # noqa: F401
+from .models import nibotar as _nibotar  # noqa: F401
 from .models.model import Model
 from .models.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from .sampling.sampler import Rng, Sampler, SamplerConfig
@@ -34,7 +36,7 @@ def __getattr__(name):
 
 
 __all__ = ["Architecture", "ConfigError", "Engine", "GenOptions", "GenResult", "LayerSpec", "Model", "ModelConfig",
-           "ModelSpec", "PartSpec", "Qwen3Config", "Rng", "SafeTensorsDir", "SafeTensorsError", "Sampler",
+           "ModelSpec", "NibotarConfig", "PartSpec", "Qwen3Config", "Rng", "SafeTensorsDir", "SafeTensorsError", "Sampler",
            "SamplerConfig", "ScheduleEntry", "WeightError", "architecture_names", "config_from_json", "generate",
            "get_architecture", "load_config", "load_weights", "register_architecture", "write_random_model",
            "write_safetensors"]

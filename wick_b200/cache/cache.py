@@ -96,7 +96,9 @@ class Storage:
 
 
 class PagedKV(Storage):
-    """Keys and values of every position: [entries, pages, 2, kv_heads, 64, head_dim]."""
+    """Keys and values of every position: [entries, pages, 2, kv_heads, 64, head_dim].  Where
+    values have a size of their own, a page is flat: [kv_heads, 64, head_dim] keys, then
+    [kv_heads, 64, v_head_dim] values (with equal sizes the two forms are the same memory)."""
     kind = "paged_kv"
 
     def __init__(self, need, n_entries, **kw):
@@ -104,15 +106,20 @@ class PagedKV(Storage):
         if need.window is not None:
             raise ValueError("paged key/value storage keeps every position; a window needs a storage kind of its own")
 
+    def _v_dim(self) -> int:
+        return self.need.head_dim if self.need.v_head_dim is None else self.need.v_head_dim
+
     def shape(self):
         n = self.need
+        if self._v_dim() != n.head_dim:
+            return (self.n_entries, self.n_pages, n.kv_heads * PAGE * (n.head_dim + self._v_dim()))
         return (self.n_entries, self.n_pages, 2, n.kv_heads, PAGE, n.head_dim)
 
     def view(self, idx, batch):
         return CacheView(kv=self.tensor[idx])
 
     def bytes_per_token(self) -> int:
-        return self.n_entries * 2 * self.need.kv_heads * self.need.head_dim * self.element_size()
+        return self.n_entries * self.need.kv_heads * (self.need.head_dim + self._v_dim()) * self.element_size()
 
     def read_bytes(self, cached_tokens, n_seqs):
         return cached_tokens * self.bytes_per_token()
@@ -164,7 +171,7 @@ class _Group:
 
     def key(self):
         n = self.need
-        return (n.kind, n.kv_heads, n.head_dim, n.window, tuple(n.shape), self.dtype)
+        return (n.kind, n.kv_heads, n.head_dim, n.v_head_dim, n.window, tuple(n.shape), self.dtype)
 
 
 class Cache:

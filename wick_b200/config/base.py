@@ -2,7 +2,8 @@
 
 A configuration is a frozen dataclass whose fields are read from the
 architecture's own ``config.json`` keys.  The registry maps the architecture
-name found in ``config.json`` (``architectures[0]``, else ``model_type``) to an
+name found in ``config.json`` (``architectures[0]``, else ``model_type``, else
+``architecture``) to an
 :class:`Architecture`: the configuration class and the function that turns a
 configuration into a :class:`~wick_b200.models.spec.ModelSpec`.
 
@@ -93,13 +94,15 @@ def get_architecture(name: str) -> Architecture:
 
 
 def architecture_name_of(j: Mapping[str, Any]) -> str:
-    """``architectures[0]`` if present, else ``model_type`` (config.rs:56-62)."""
+    """``architectures[0]`` if present, else ``model_type`` (config.rs:56-62), else a
+    single ``architecture`` name."""
     archs = j.get("architectures")
     if isinstance(archs, list) and archs and isinstance(archs[0], str):
         return archs[0]
-    mt = j.get("model_type")
-    if isinstance(mt, str):
-        return mt
+    for key in ("model_type", "architecture"):
+        mt = j.get(key)
+        if isinstance(mt, str):
+            return mt
     raise ConfigError("config.json has no architectures")
 
 

@@ -1,0 +1,248 @@
+// Attention with options, for any head sizes (run-time numbers): projection biases, an
+// RMS norm of q and k over spans of any length (a head, or the whole projection), a
+// rotation of neighbouring or of half-split pairs over the first dims of each head, values
+// blended with the values another layer made for the same token, key and value heads of
+// different sizes, a visibility rule (all earlier keys, the query's own block of positions,
+// or the last positions), and a sink in the softmax's denominator.
+//
+//   finish  : the q/k/v projection's float32 partial sums -> q (activation type) and the
+//             token's key and value in its sequence's cache page
+//   attend  : every new token over the cache, one warp per (token, query head)
+//
+// Cache page of one schedule entry: [kv_head][64][d] keys, then [kv_head][64][e] values.
+// Scores, the softmax, its weights and the weighted sum are float32.  A token's work is the
+// same whatever else the step holds: keys are walked 32 at a time from the first visible one.
+#include "common.cuh"
+
+namespace wick {
+
+constexpr int MASK_CAUSAL = 0, MASK_BLOCK = 1, MASK_WINDOW = 2;
+
+// First key that the query at position p sees.
+__device__ __forceinline__ int first_visible(int p, int mask, int size) {
+    if (mask == MASK_BLOCK) return p / size * size;
+    if (mask == MASK_WINDOW) return max(0, p - size + 1);
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// One block per token.  The row [q | k | v] (H d + G d + G e numbers) is summed into shared
+// memory; then, in this order: biases, the norms (a warp per span), the rotation, the value
+// blend, and the stores.
+//   v_mode 0: values as projected; 1: also kept in v_keep [n, G e] (float32) for later layers;
+//   2: v <- (1 - lambda) v + lambda v_keep.
+//   pairing 0: (2i, 2i + 1) rotate together; 1: (i, i + rot_dims / 2).
+template <typename T>
+__global__ void __launch_bounds__(256)
+qkv_finish_kernel(const float* __restrict__ parts, int splits, int64_t split_stride, const float* __restrict__ bias,
+                  int H, int G, int d, int e, const float* __restrict__ q_w, int q_span, const float* __restrict__ k_w,
+                  int k_span, float eps, const float* __restrict__ inv_freq, int rot_dims, int pairing,
+                  float* __restrict__ v_keep, int v_mode, const float* __restrict__ lambda, T* __restrict__ q_out,
+                  T* __restrict__ kv, const int* __restrict__ page_table, int table_width,
+                  const int* __restrict__ seq_of_token, const int* __restrict__ positions, int write_kv) {
+    extern __shared__ float row[];
+    pdl_trigger();
+    pdl_wait();
+    parts = fresh(parts);
+    v_keep = fresh(v_keep);
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
+    const int Wq = H * d, Wk = G * d, Wv = G * e, W = Wq + Wk + Wv;
+    for (int j = tid; j < W; j += blockDim.x) {
+        float v = parts[(int64_t)t * W + j];
+        for (int s = 1; s < splits; ++s) v += parts[s * split_stride + (int64_t)t * W + j];
+        if (bias) v += bias[j];
+        row[j] = v;
+    }
+    __syncthreads();
+    const int nq = q_w ? Wq / q_span : 0, nk = k_w ? Wk / k_span : 0;
+    for (int seg = warp; seg < nq + nk; seg += n_warps) {
+        const bool is_q = seg < nq;
+        const int span = is_q ? q_span : k_span;
+        float* p = row + (is_q ? seg * q_span : Wq + (seg - nq) * k_span);
+        const float* w = is_q ? q_w : k_w;
+        float ss = 0.f;
+        for (int j = lane; j < span; j += 32) ss = fmaf(p[j], p[j], ss);
+        ss = warp_sum(ss);
+        const float scale = 1.0f / sqrtf(ss / (float)span + eps);
+        for (int j = lane; j < span; j += 32) p[j] = (p[j] * scale) * w[j];
+    }
+    __syncthreads();
+    const int pos = positions[t];
+    if (inv_freq && rot_dims > 0) {
+        const int half = rot_dims >> 1;
+        for (int idx = tid; idx < (H + G) * half; idx += blockDim.x) {
+            const int h = idx / half, i = idx - h * half;
+            float* p = row + h * d;                       // (the k heads follow the q heads at the same stride)
+            const int j0 = pairing == 0 ? 2 * i : i, j1 = pairing == 0 ? 2 * i + 1 : i + half;
+            float sn, cs;
+            sincosf((float)pos * inv_freq[i], &sn, &cs);
+            const float u = p[j0], v = p[j1];
+            p[j0] = u * cs - v * sn;
+            p[j1] = v * cs + u * sn;
+        }
+    }
+    __syncthreads();
+    for (int j = tid; j < Wq; j += blockDim.x) st(q_out + (int64_t)t * Wq + j, row[j]);
+    const float lam = v_mode == 2 ? *lambda : 0.f;
+    T* page = nullptr;
+    if (write_kv) {
+        const int pg = page_table[(int64_t)seq_of_token[t] * table_width + pos / kPage];
+        page = kv + (int64_t)pg * G * kPage * (d + e);
+    }
+    const int r = pos % kPage;
+    for (int j = tid; j < Wk && write_kv; j += blockDim.x) {
+        const int g = j / d, x = j - g * d;
+        st(page + ((int64_t)g * kPage + r) * d + x, row[Wq + j]);
+    }
+    for (int j = tid; j < Wv; j += blockDim.x) {
+        float v = row[Wq + Wk + j];
+        if (v_mode == 1) v_keep[(int64_t)t * Wv + j] = v;
+        if (v_mode == 2) v = (1.0f - lam) * v + lam * v_keep[(int64_t)t * Wv + j];
+        if (write_kv) {
+            const int g = j / e, x = j - g * e;
+            st(page + (int64_t)G * kPage * d + ((int64_t)g * kPage + r) * e + x, v);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// One warp per (token, query head).  32 keys at a time: lane l scores key j0 + l (a dot
+// product of d numbers, in index order), the running maximum and sum follow, then every
+// lane adds the 32 weighted value rows into its elements l, l + 32, ... of the result.
+// A sink starts the running maximum at its value and the sum at 1: a key with that score
+// and no value.
+constexpr int E_PER_LANE = 8;                  // value sizes up to 256
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+attn_masked_kernel(const T* __restrict__ q, const T* __restrict__ kv, T* __restrict__ out,
+                   const int* __restrict__ seq_of_token, const int* __restrict__ positions,
+                   const int* __restrict__ page_table, int table_width, int n_tokens, int H, int G, int d, int e,
+                   float scale, int mask, int mask_size, const float* __restrict__ sink) {
+    extern __shared__ float qs_all[];
+    pdl_trigger();
+    pdl_wait();
+    q = fresh(q);
+    kv = fresh(kv);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t id = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (id >= (int64_t)n_tokens * H) return;
+    const int t = (int)(id / H), h = (int)(id - (int64_t)t * H);
+    const int g = h / (H / G);
+    const int pos = positions[t];
+    const int* table = page_table + (int64_t)seq_of_token[t] * table_width;
+    float* qs = qs_all + warp * d;
+    for (int x = lane; x < d; x += 32) qs[x] = ld(q + ((int64_t)t * H + h) * d + x);
+    __syncwarp();
+    const int64_t page_elems = (int64_t)G * kPage * (d + e);
+    const int64_t v_off = (int64_t)G * kPage * d;
+    float m = sink ? sink[h] : -INFINITY, l = sink ? 1.f : 0.f;
+    float acc[E_PER_LANE];
+#pragma unroll
+    for (int c = 0; c < E_PER_LANE; ++c) acc[c] = 0.f;
+    for (int j0 = first_visible(pos, mask, mask_size); j0 <= pos; j0 += 32) {
+        const int j = j0 + lane;
+        float s = -INFINITY;
+        if (j <= pos) {
+            const T* kp = kv + table[j / kPage] * page_elems + ((int64_t)g * kPage + (j % kPage)) * d;
+            float dot = 0.f;
+            for (int x = 0; x < d; ++x) dot = fmaf(qs[x], ld(kp + x), dot);
+            s = dot * scale;
+        }
+        const float m_new = fmaxf(m, warp_max(s));            // finite: key j0 is visible
+        const float corr = expf(m - m_new);                    // (m = -inf at first without a sink: 0)
+        const float p = j <= pos ? expf(s - m_new) : 0.f;
+        l = l * corr + warp_sum(p);
+        m = m_new;
+#pragma unroll
+        for (int c = 0; c < E_PER_LANE; ++c) acc[c] *= corr;
+        const int n_keys = min(32, pos - j0 + 1);
+        for (int jj = 0; jj < n_keys; ++jj) {
+            const float pj = __shfl_sync(0xffffffffu, p, jj);
+            const int key = j0 + jj;
+            const T* vp = kv + table[key / kPage] * page_elems + v_off + ((int64_t)g * kPage + (key % kPage)) * e;
+#pragma unroll
+            for (int c = 0; c < E_PER_LANE; ++c) {
+                const int x = lane + 32 * c;
+                if (x < e) acc[c] = fmaf(pj, ld(vp + x), acc[c]);
+            }
+        }
+    }
+    const float inv = 1.0f / l;
+#pragma unroll
+    for (int c = 0; c < E_PER_LANE; ++c) {
+        const int x = lane + 32 * c;
+        if (x < e) st(out + ((int64_t)t * H + h) * e + x, acc[c] * inv);
+    }
+}
+
+template <typename T>
+int qkv_finish(const float* parts, int splits, int n, const float* bias, int H, int G, int d, int e, const float* q_w,
+               int q_span, const float* k_w, int k_span, float eps, const float* inv_freq, int rot_dims, int pairing,
+               float* v_keep, int v_mode, const float* lambda, void* q_out, void* kv, const int* page_table, int table_width,
+               const int* seq_of_token, const int* positions, int write_kv, cudaStream_t s) {
+    WICK_REQUIRE(H > 0 && G > 0 && H % G == 0 && d > 0 && e > 0, "qkv_finish: bad head counts or sizes");
+    WICK_REQUIRE(splits >= 1, "qkv_finish: partial sums are needed");
+    const int Wq = H * d, Wk = G * d;
+    if (q_w) WICK_REQUIRE(q_span > 0 && Wq % q_span == 0, "qkv_finish: a q norm span of %d does not divide %d", q_span, Wq);
+    if (k_w) WICK_REQUIRE(k_span > 0 && Wk % k_span == 0, "qkv_finish: a k norm span of %d does not divide %d", k_span, Wk);
+    WICK_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= d, "qkv_finish: %d rotated dims of %d", rot_dims, d);
+    WICK_REQUIRE(v_mode == 0 || v_keep, "qkv_finish: the kept values are missing");
+    WICK_REQUIRE(v_mode != 2 || lambda, "qkv_finish: the blend factor is missing");
+    if (n == 0) return 0;
+    const size_t smem = (size_t)(Wq + Wk + G * e) * sizeof(float);
+    WICK_REQUIRE(smem <= 200 * 1024, "qkv_finish: a row of %d numbers is beyond one block's shared memory", Wq + Wk + G * e);
+    static bool raised = false;
+    if (smem > 48 * 1024 && !raised) {
+        WICK_CUDA(cudaFuncSetAttribute(qkv_finish_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        raised = true;
+    }
+    WICK_CUDA(launch(qkv_finish_kernel<T>, dim3(n), dim3(256), smem, s, parts, splits, (int64_t)n * (Wq + Wk + G * e), bias, H, G,
+                     d, e, q_w, q_span, k_w, k_span, eps, inv_freq, rot_dims, pairing, v_keep, v_mode, lambda, (T*)q_out,
+                     (T*)kv, page_table, table_width, seq_of_token, positions, write_kv));
+    return check_launch("qkv_finish");
+}
+
+template <typename T>
+int attn_masked(const void* q, const void* kv, void* out, const int* seq_of_token, const int* positions,
+                const int* page_table, int table_width, int n, int H, int G, int d, int e, float scale, int mask,
+                int mask_size, const float* sink, cudaStream_t s) {
+    WICK_REQUIRE(H > 0 && G > 0 && H % G == 0 && d > 0 && e > 0, "attn_masked: bad head counts or sizes");
+    WICK_REQUIRE(e <= 32 * E_PER_LANE, "attn_masked: a value size of %d is beyond %d", e, 32 * E_PER_LANE);
+    WICK_REQUIRE(mask == MASK_CAUSAL || mask_size > 0, "attn_masked: the mask needs a positive size");
+    if (n == 0) return 0;
+    const int warps = 4;
+    const size_t smem = (size_t)warps * d * sizeof(float);
+    WICK_REQUIRE(smem <= 48 * 1024, "attn_masked: a head size of %d is beyond %d", d, 48 * 1024 / 4 / warps);
+    WICK_CUDA(launch(attn_masked_kernel<T>, dim3(ceil_div((int64_t)n * H, warps)), dim3(warps * 32), smem, s, (const T*)q,
+                     (const T*)kv, (T*)out, seq_of_token, positions, page_table, table_width, n, H, G, d, e, scale, mask,
+                     mask_size, sink));
+    return check_launch("attn_masked");
+}
+
+}  // namespace wick
+
+using namespace wick;
+typedef __nv_bfloat16 bf16;
+
+#define WICK_QKV_FINISH(NAME, T)                                                                                              \
+    WICK_API int NAME(const float* parts, int splits, int n, const float* bias, int H, int G, int d, int e, const float* q_w,    \
+                      int q_span, const float* k_w, int k_span, float eps, const float* inv_freq, int rot_dims, int pairing,     \
+                      float* v_keep, int v_mode, const float* lambda, void* q_out, void* kv, const int* page_table,              \
+                      int table_width, const int* seq_of_token, const int* positions, int write_kv, void* s) {                   \
+        return qkv_finish<T>(parts, splits, n, bias, H, G, d, e, q_w, q_span, k_w, k_span, eps, inv_freq, rot_dims, pairing,      \
+                             v_keep, v_mode, lambda, q_out, kv, page_table, table_width, seq_of_token, positions, write_kv,      \
+                             (cudaStream_t)s);                                                                                   \
+    }
+WICK_QKV_FINISH(wick_qkv_finish_bf16, bf16)
+WICK_QKV_FINISH(wick_qkv_finish_f32, float)
+
+#define WICK_ATTN_MASKED(NAME, T)                                                                                             \
+    WICK_API int NAME(const void* q, const void* kv, void* out, const int* seq_of_token, const int* positions,                 \
+                      const int* page_table, int table_width, int n, int H, int G, int d, int e, float scale, int mask,        \
+                      int mask_size, const float* sink, void* s) {                                                             \
+        return attn_masked<T>(q, kv, out, seq_of_token, positions, page_table, table_width, n, H, G, d, e, scale, mask,        \
+                              mask_size, sink, (cudaStream_t)s);                                                               \
+    }
+WICK_ATTN_MASKED(wick_attn_masked_bf16, bf16)
+WICK_ATTN_MASKED(wick_attn_masked_f32, float)

@@ -1,0 +1,126 @@
+// Row-wise kernels of layers that normalise AFTER the residual sum, and two
+// element-wise steps: the squared ReLU of a plain feed-forward and the soft cap of
+// logits.  All arithmetic is float32; T is the storage type of activations.
+//
+//   post-norm :  y = rms(alpha * x + d_0 + d_1 + ...) * g,   rms(v) = v / sqrt(mean(v^2) + eps)
+//                y replaces x (float32, the residual stream) and is also written
+//                in the activation type for the next matrix product.
+//   relu^2    :  a <- max(a, 0)^2
+//   soft cap  :  z <- c * tanh(z / c)
+#include "common.cuh"
+
+namespace wick {
+
+// One warp per row.  First pass: v = alpha x + sum of the partial sums (index order) goes
+// back to x and its squares are summed (lane l takes elements l, l + 32, ...; the 32 sums by
+// the butterfly); second pass: the same lane reads its own v again and writes y.  The order
+// of every sum depends on the width alone, so a row's bits do not depend on the batch.
+template <typename TOut>
+__global__ void __launch_bounds__(128)
+scaled_add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int splits, int64_t split_stride,
+                          float alpha, const float* __restrict__ w, float eps, TOut* __restrict__ out, int n, int width) {
+    pdl_trigger();
+    pdl_wait();
+    x = fresh(x);
+    delta = fresh(delta);
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= n) return;
+    float* xr = x + (int64_t)r * width;
+    float ss = 0.f;
+    for (int j = lane; j < width; j += 32) {
+        float v = alpha * xr[j];
+        for (int s = 0; s < splits; ++s) v += delta[s * split_stride + (int64_t)r * width + j];
+        xr[j] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    TOut* o = out ? out + (int64_t)r * width : nullptr;
+    for (int j = lane; j < width; j += 32) {
+        const float y = (xr[j] * scale) * w[j];
+        xr[j] = y;
+        if (o) st(o + j, y);
+    }
+}
+
+template <typename T>
+__global__ void relu_squared_kernel(T* __restrict__ a, int64_t n) {
+    pdl_trigger();
+    pdl_wait();
+    a = fresh(a);
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = fmaxf(ld(a + i), 0.f);
+    st(a + i, v * v);
+}
+
+__global__ void soft_cap_kernel(float* __restrict__ z, int64_t n, float cap) {
+    pdl_trigger();
+    pdl_wait();
+    z = fresh(z);
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    z[i] = cap * tanhf(z[i] / cap);
+}
+
+// float32 -> activation type (the residual stream as the input of a matrix product).
+template <typename T>
+__global__ void to_activation_kernel(const float* __restrict__ x, T* __restrict__ out, int64_t n) {
+    pdl_trigger();
+    pdl_wait();
+    x = fresh(x);
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) st(out + i, x[i]);
+}
+
+template <typename TOut>
+int scaled_add_rmsnorm(float* x, const float* delta, int splits, float alpha, const float* w, float eps, void* out, int n,
+                       int width, cudaStream_t s) {
+    WICK_REQUIRE(width > 0 && n >= 0 && splits >= 0, "scaled_add_rmsnorm: bad sizes");
+    if (n == 0) return 0;
+    WICK_CUDA(launch(scaled_add_rmsnorm_kernel<TOut>, dim3(ceil_div(n, 4)), dim3(128), 0, s, x, delta, splits,
+                     (int64_t)n * width, alpha, w, eps, (TOut*)out, n, width));
+    return check_launch("scaled_add_rmsnorm");
+}
+
+}  // namespace wick
+
+using namespace wick;
+typedef __nv_bfloat16 bf16;
+
+// x: float32 [n, width], replaced by the normalised rows; delta: float32 [splits, n, width] or
+// null; w: float32 [width] (the factor itself: an offset is added by the caller); out: [n, width]
+// in the activation type or null.
+WICK_API int wick_scaled_add_rmsnorm_bf16(float* x, const float* delta, int splits, float alpha, const float* w, float eps,
+                                          void* out, int n, int width, void* s) {
+    return scaled_add_rmsnorm<bf16>(x, delta, splits, alpha, w, eps, out, n, width, (cudaStream_t)s);
+}
+WICK_API int wick_scaled_add_rmsnorm_f32(float* x, const float* delta, int splits, float alpha, const float* w, float eps,
+                                         void* out, int n, int width, void* s) {
+    return scaled_add_rmsnorm<float>(x, delta, splits, alpha, w, eps, out, n, width, (cudaStream_t)s);
+}
+
+WICK_API int wick_relu_squared_bf16(void* a, int64_t n, void* s) {
+    if (n == 0) return 0;
+    WICK_CUDA(launch(relu_squared_kernel<bf16>, dim3(ceil_div(n, 256)), dim3(256), 0, (cudaStream_t)s, (bf16*)a, n));
+    return check_launch("relu_squared");
+}
+WICK_API int wick_relu_squared_f32(void* a, int64_t n, void* s) {
+    if (n == 0) return 0;
+    WICK_CUDA(launch(relu_squared_kernel<float>, dim3(ceil_div(n, 256)), dim3(256), 0, (cudaStream_t)s, (float*)a, n));
+    return check_launch("relu_squared");
+}
+
+WICK_API int wick_soft_cap(float* z, int64_t n, float cap, void* s) {
+    WICK_REQUIRE(cap > 0.f, "soft_cap: the cap must be positive");
+    if (n == 0) return 0;
+    WICK_CUDA(launch(soft_cap_kernel, dim3(ceil_div(n, 256)), dim3(256), 0, (cudaStream_t)s, z, n, cap));
+    return check_launch("soft_cap");
+}
+
+WICK_API int wick_to_activation_bf16(const float* x, void* out, int64_t n, void* s) {
+    if (n == 0) return 0;
+    WICK_CUDA(launch(to_activation_kernel<bf16>, dim3(ceil_div(n, 256)), dim3(256), 0, (cudaStream_t)s, x, (bf16*)out, n));
+    return check_launch("to_activation");
+}

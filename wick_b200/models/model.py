@@ -14,6 +14,7 @@ import torch
 
 from ..parts.base import Block, BuildContext, CacheNeed, Hidden, Part, TensorSpec, build_part
 from ..parts import standard as _standard_parts   # registers the standard kinds  # noqa: F401
+from ..parts import attention as _attention_parts, feedforward as _feedforward_parts   # noqa: F401
 from .spec import ModelSpec
 
 

@@ -519,6 +519,181 @@ def attention_decode_parts_fused(qkv: torch.Tensor, n_heads: int, n_kv: int, hea
 
 
 # ---------------------------------------------------------------------------
+# Mechanisms of layers beyond the plain pre-norm decoder: the norm after the residual sum, a
+# feed-forward's squared ReLU, the soft cap of logits, attention with options (csrc/attn_masked.cu)
+# and experts chosen by a table (csrc/moe.cu).
+LAYER_SOURCES = ["layer_ops.cu", "attn_masked.cu", "moe.cu"]
+
+MASKS = {"causal": 0, "block": 1, "window": 2}
+PAIRINGS = {"neighbours": 0, "halves": 1}
+
+
+def _layer() -> _Lib:
+    lib = _libs.get("layer")
+    if lib is None:
+        lib = _libs["layer"] = _Lib("wick_layer", LAYER_SOURCES)
+    return lib
+
+
+def scaled_add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], alpha: float, weight: torch.Tensor, eps: float,
+                       out_dtype: torch.dtype) -> Optional[torch.Tensor]:
+    """x <- rms(alpha * x + delta[0] + delta[1] + ...) * weight, in place (float32 [n, width]).
+    Returns the same rows in ``out_dtype``; for float32 that is ``x`` itself."""
+    _cuda("x", x, torch.float32)
+    n, width = x.shape
+    _cuda("weight", weight, torch.float32, (width,))
+    splits = 0
+    if delta is not None:
+        _cuda("delta", delta, torch.float32)
+        _need(delta.dim() == 3 and tuple(delta.shape[1:]) == (n, width),
+              f"delta must be [splits, {n}, {width}], is {tuple(delta.shape)}")
+        splits = delta.shape[0]
+    out = None if out_dtype == torch.float32 else torch.empty((n, width), dtype=out_dtype, device=x.device)
+    name = "wick_scaled_add_rmsnorm_f32" if out is None else f"wick_scaled_add_rmsnorm_{_dt(out)}"
+    _layer().call(name, "ppifpfpiip", _p(x), _p(delta), splits, float(alpha), _p(weight), float(eps), _p(out), n, width,
+                  _stream())
+    return x if out is None else out
+
+
+def relu_squared_(a: torch.Tensor) -> torch.Tensor:
+    """a <- max(a, 0)^2 in place."""
+    _cuda("a", a)
+    _layer().call(f"wick_relu_squared_{_dt(a)}", "plp", _p(a), a.numel(), _stream())
+    return a
+
+
+def soft_cap_(z: torch.Tensor, cap: float) -> torch.Tensor:
+    """z <- cap * tanh(z / cap) in place (float32)."""
+    _cuda("z", z, torch.float32)
+    _layer().call("wick_soft_cap", "plfp", _p(z), z.numel(), float(cap), _stream())
+    return z
+
+
+def to_activation(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """float32 -> the activation type (float32: ``x`` itself)."""
+    _cuda("x", x, torch.float32)
+    if dtype == torch.float32:
+        return x
+    _need(dtype == torch.bfloat16, f"no conversion to {dtype}")
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    _layer().call("wick_to_activation_bf16", "pplp", _p(x), _p(out), x.numel(), _stream())
+    return out
+
+
+def _kv_pages(name: str, kv: torch.Tensor, dtype, n_kv: int, d: int, e: int) -> None:
+    _cuda(name, kv, dtype)
+    per_page = n_kv * PAGE * (d + e)
+    _need(kv.dim() >= 2 and kv[0].numel() == per_page,
+          f"{name} must hold pages of {n_kv} x {PAGE} x ({d} + {e}) elements, is {tuple(kv.shape)}")
+
+
+def qkv_finish(parts: torch.Tensor, n_heads: int, n_kv: int, d: int, e: int, *, dtype: torch.dtype,
+               bias: Optional[torch.Tensor] = None, q_weight: Optional[torch.Tensor] = None,
+               k_weight: Optional[torch.Tensor] = None, eps: float = 0.0, inv_freq: Optional[torch.Tensor] = None,
+               rot_dims: int = 0, pairing: str = "neighbours", v_keep: Optional[torch.Tensor] = None, v_mode: int = 0,
+               blend: Optional[torch.Tensor] = None, kv: Optional[torch.Tensor], page_table: torch.Tensor,
+               seq_of_token: torch.Tensor, positions: torch.Tensor, write_kv: bool = True) -> torch.Tensor:
+    """From the q/k/v projection's float32 partial sums ``parts`` [splits, n, H d + G d + G e]:
+    biases, RMS norms of q and k over spans the length of their weight vectors (a head, or the
+    whole projection), rotation of the first ``rot_dims`` elements of every q and k head by
+    ``position * inv_freq[i]`` (``pairing``: which two elements turn together), the value blend
+    (``v_mode`` 1: the values are also kept in ``v_keep`` [n, G e]; 2: v <- (1 - blend) v + blend
+    v_keep), then q -> the result [n, H, d] in ``dtype`` and k, v -> the token's place in ``kv``."""
+    _cuda("parts", parts, torch.float32)
+    W = (n_heads + n_kv) * d + n_kv * e
+    _need(parts.dim() == 3 and parts.shape[2] == W, f"parts must be [splits, n, {W}], is {tuple(parts.shape)}")
+    n = parts.shape[1]
+    if bias is not None:
+        _cuda("bias", bias, torch.float32, (W,))
+    q_span = k_span = 0
+    if q_weight is not None:
+        _cuda("q_weight", q_weight, torch.float32)
+        q_span = q_weight.numel()
+    if k_weight is not None:
+        _cuda("k_weight", k_weight, torch.float32)
+        k_span = k_weight.numel()
+    if inv_freq is not None:
+        _cuda("inv_freq", inv_freq, torch.float32, (rot_dims // 2,))
+    if v_mode:
+        _cuda("v_keep", v_keep, torch.float32, (n, n_kv * e))
+    if v_mode == 2:
+        _cuda("blend", blend, torch.float32)
+        _need(blend.numel() == 1, "the blend factor is one number")
+    if write_kv:
+        _kv_pages("kv", kv, dtype, n_kv, d, e)
+    _cuda("page_table", page_table, torch.int32)
+    _cuda("seq_of_token", seq_of_token, torch.int32, (n,))
+    _cuda("positions", positions, torch.int32, (n,))
+    q_out = torch.empty((n, n_heads, d), dtype=dtype, device=parts.device)
+    _layer().call(f"wick_qkv_finish_{_dt(q_out)}", "piipiiiipipifpiipippppippip", _p(parts), parts.shape[0], n, _p(bias),
+                  n_heads, n_kv, d, e, _p(q_weight), q_span, _p(k_weight), k_span, float(eps), _p(inv_freq),
+                  rot_dims if inv_freq is not None else 0, PAIRINGS[pairing], _p(v_keep), v_mode, _p(blend), _p(q_out),
+                  _p(kv) if write_kv else None, _p(page_table), page_table.shape[-1], _p(seq_of_token), _p(positions),
+                  1 if write_kv else 0, _stream())
+    return q_out
+
+
+def attention_masked(q: torch.Tensor, kv: torch.Tensor, batch, scale: float, *, n_kv: int, v_dim: int,
+                     mask: str = "causal", mask_size: int = 0, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of the step's tokens (a prompt's or one per sequence) over the cache, which
+    already holds their keys and values.  q: [n, H, d]; result [n, H, v_dim].  ``mask``:
+    ``causal`` (every earlier key), ``block`` (earlier keys in the query's own block of
+    ``mask_size`` positions, blocks counted from position 0) or ``window`` (the last
+    ``mask_size`` positions).  ``sink``: float32 [H], a score per head that joins the
+    softmax's denominator without a value."""
+    _cuda("q", q)
+    n, n_heads, d = q.shape
+    _kv_pages("kv", kv, q.dtype, n_kv, d, v_dim)
+    _need(n == batch.n_tokens, f"q has {n} rows, the batch {batch.n_tokens} tokens")
+    if sink is not None:
+        _cuda("sink", sink, torch.float32, (n_heads,))
+    out = torch.empty((n, n_heads, v_dim), dtype=q.dtype, device=q.device)
+    _layer().call(f"wick_attn_masked_{_dt(q)}", "ppppppiiiiiifiipp", _p(q), _p(kv), _p(out), _p(batch.seq_of_token),
+                  _p(batch.positions), _p(batch.page_table), batch.table_width, n, n_heads, n_kv, d, v_dim, float(scale),
+                  MASKS[mask], int(mask_size), _p(sink), _stream())
+    return out
+
+
+def moe_table_up(x: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
+    """hidden[t, c] = silu(gate x_t) * (up x_t) with the matrices of expert ``table[tokens[t], c]``.
+    x [n, width]; table int32 [vocab, top]; gate_up [experts, 2, ff, width] -> [n, top, ff]."""
+    _cuda("x", x)
+    n, width = x.shape
+    _cuda("tokens", tokens, torch.int32, (n,))
+    _cuda("table", table, torch.int32)
+    _cuda("gate_up", gate_up, x.dtype)
+    _need(gate_up.dim() == 4 and gate_up.shape[1] == 2 and gate_up.shape[3] == width, "gate_up must be [experts, 2, ff, width]")
+    top, ff = table.shape[1], gate_up.shape[2]
+    hidden = torch.empty((n, top, ff), dtype=x.dtype, device=x.device)
+    _layer().call(f"wick_moe_up_{_dt(x)}", "pppiippiiip", _p(x), _p(tokens), _p(table), top, gate_up.shape[0], _p(gate_up),
+                  _p(hidden), n, width, ff, _stream())
+    return hidden
+
+
+def moe_table_down(hidden: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, down: torch.Tensor, weight: float,
+                   base: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """float32 out[t] = sum(base[:, t]) + weight * sum over c of down[table[tokens[t], c]] hidden[t, c].
+    down [experts, width, ff]; base float32 [splits, n, width] or None."""
+    _cuda("hidden", hidden)
+    n, top, ff = hidden.shape
+    _cuda("tokens", tokens, torch.int32, (n,))
+    _cuda("table", table, torch.int32)
+    _need(table.shape[1] == top, "the table's width is the number of choices")
+    _cuda("down", down, hidden.dtype)
+    _need(down.dim() == 3 and down.shape[2] == ff, "down must be [experts, width, ff]")
+    width = down.shape[1]
+    splits = 0
+    if base is not None:
+        _cuda("base", base, torch.float32)
+        _need(base.dim() == 3 and tuple(base.shape[1:]) == (n, width), f"base must be [splits, {n}, {width}]")
+        splits = base.shape[0]
+    out = torch.empty((n, width), dtype=torch.float32, device=hidden.device)
+    _layer().call(f"wick_moe_down_{_dt(hidden)}", "pppiipfpipiiip", _p(hidden), _p(tokens), _p(table), top, down.shape[0],
+                  _p(down), float(weight), _p(base), splits, _p(out), n, width, ff, _stream())
+    return out
+
+
+# ---------------------------------------------------------------------------
 def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """First index of each row's maximum (int32 [rows])."""
     _cuda("logits", logits, torch.float32)

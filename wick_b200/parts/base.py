@@ -35,12 +35,20 @@ class TensorSpec:
     ``vector``: always float32 (norm weights and the like: tensors that a
     checkpoint stores in 32-bit stay 32-bit, and 16-bit vectors are widened
     exactly, as wick does for every 1-D tensor, model.rs:136-142);
-    ``table``: integers, as int32."""
+    ``table``: integers, as int32.
+
+    ``init`` tells the random-weights writer what a sensible value looks like where the
+    role's default (matrices N(0, std), vectors 1 + N(0, vector_std)) is none:
+    ``around_zero`` (a vector that is added, or a norm weight stored as its distance from
+    one), ``unit_interval`` (a blend factor), ``distinct_below`` (integer rows of different
+    values below ``init_arg``)."""
 
     name: str
     shape: Tuple[int, ...]
     role: str = "matrix"
     optional: bool = False
+    init: str = ""
+    init_arg: int = 0
 
 
 @dataclasses.dataclass(frozen=True)
@@ -71,8 +79,8 @@ class CacheNeed:
     """What a mixer asks of the cache for one schedule entry.
 
     kind ``paged_kv``: keys and values of every position, ``kv_heads`` x
-    ``head_dim`` each, in pages; ``window`` (tokens) if only the last ones are
-    ever read.  kind ``state``: one record of fixed ``shape`` and ``dtype`` per
+    ``head_dim`` each, in pages (values ``v_head_dim`` each, if that is given and
+    differs); ``window`` (tokens) if only the last ones are ever read.  kind ``state``: one record of fixed ``shape`` and ``dtype`` per
     sequence, zeroed when the sequence starts."""
 
     kind: str
@@ -81,6 +89,7 @@ class CacheNeed:
     window: Optional[int] = None
     shape: Tuple[int, ...] = ()
     dtype: Optional[torch.dtype] = None   # None: the compute dtype
+    v_head_dim: Optional[int] = None      # None: as head_dim
 
 
 class Part:
@@ -141,6 +150,17 @@ class Norm(Part):
         x.add_(delta.sum(0) if delta.shape[0] > 1 else delta[0])
         return self.forward(x, out_dtype, rows)
 
+    def scaled_add_forward(self, x: torch.Tensor, delta: Optional[torch.Tensor], alpha: float,
+                           out_dtype: torch.dtype) -> torch.Tensor:
+        """The norm AFTER the sum: ``x <- norm(alpha * x + sum(delta))`` in float32 and in
+        place (``delta`` [splits, n, width] or None); returns the new rows in ``out_dtype``
+        (for float32, ``x`` itself)."""
+        x.mul_(alpha)
+        if delta is not None:
+            x.add_(delta.sum(0) if delta.shape[0] > 1 else delta[0])
+        x.copy_(self.forward(x, torch.float32))
+        return x if out_dtype == torch.float32 else x.to(out_dtype)
+
 
 class Position(Part):
     category = "position"
@@ -188,12 +208,14 @@ class FeedForward(Part):
 class Hidden:
     """The residual stream between blocks: float32 ``x`` [tokens, width] and a
     float32 ``pending`` [splits, tokens, width] that has still to be added to it
-    (kept apart so that the next norm's kernel can do the addition)."""
+    (kept apart so that the next norm's kernel can do the addition).  ``act`` is ``x``
+    in the compute dtype where a block has made that copy (blocks whose sublayers read
+    the stream itself), else None."""
 
-    __slots__ = ("x", "pending")
+    __slots__ = ("x", "pending", "act")
 
     def __init__(self, x: torch.Tensor, pending: Optional[torch.Tensor] = None):
-        self.x, self.pending = x, pending
+        self.x, self.pending, self.act = x, pending, None
 
     def resolved(self) -> torch.Tensor:
         if self.pending is not None:

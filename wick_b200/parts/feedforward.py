@@ -1,0 +1,164 @@
+"""Feed-forwards beside the gated one of ``parts/standard.py``.
+
+=============  ======================  ==========================================
+category       kind                    params
+=============  ======================  ==========================================
+ffn            ``none``                — (a layer without a feed-forward)
+ffn            ``mlp``                 width, intermediate, activation
+                                       (``relu2``: the square of relu),
+                                       names (up, down -> local names)
+ffn            ``table_moe``           width, vocab, experts, top, intermediate,
+                                       shared (PartSpec of a feed-forward that
+                                       runs for every token, or None),
+                                       names (expert: a pattern with ``{i}``,
+                                       gate, up, down, table, shared: a prefix)
+=============  ======================  ==========================================
+
+``table_moe``: a mixture of gated experts without a router.  An integer table
+[vocab, top] names, for every token id, the ``top`` different experts that its tokens
+use; each weighs 1/top.  Expert i is down_i(silu(gate_i h) * (up_i h)), no biases.
+The result is the weighted sum of the chosen experts' results plus, if there is one,
+the shared part's.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import ops
+from .base import FeedForward, TensorSpec, build_part, register_part
+from .linear import Linear
+
+
+class NoFeedForward(FeedForward):
+    PROMPT_CAPTURABLE = True
+    IS_NONE = True
+
+    def forward(self, x, batch):
+        return torch.zeros((1,) + tuple(x.shape), dtype=torch.float32, device=x.device)
+
+
+class MLP(FeedForward):
+    """down(act(up x)), no biases."""
+
+    PROMPT_CAPTURABLE = True
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.width, self.intermediate = int(params["width"]), int(params["intermediate"])
+        self.activation = str(params.get("activation", "relu2"))
+        if self.activation != "relu2":
+            raise ValueError(f"unsupported activation {self.activation} (relu2)")
+        names = dict(up="up_proj.weight", down="down_proj.weight")
+        names.update(params.get("names") or {})
+        self.names = names
+        self.up = Linear(self.intermediate, self.width, ctx)
+        self.down = Linear(self.width, self.intermediate, ctx)
+
+    def tensor_specs(self):
+        return [TensorSpec(self.names["up"], (self.intermediate, self.width)),
+                TensorSpec(self.names["down"], (self.width, self.intermediate))]
+
+    def load(self, fetch):
+        self.up.load_rows([fetch(self.names["up"])])
+        self.down.load_rows([fetch(self.names["down"])])
+
+    def tensor(self, name):
+        if name == self.names["up"]:
+            return self.up.rows(0, self.intermediate)
+        return self.down.rows(0, self.width) if name == self.names["down"] else None
+
+    def weight_bytes(self):
+        return self.up.weight_bytes() + self.down.weight_bytes()
+
+    def forward(self, x, batch):
+        a = ops.relu_squared_(self.up.forward(x, self.ctx.dtype))
+        return self.down.forward_delta(a)
+
+
+class TableMoE(FeedForward):
+    PROMPT_CAPTURABLE = True
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        p = params
+        self.width, self.vocab = int(p["width"]), int(p["vocab"])
+        self.experts, self.top, self.intermediate = int(p["experts"]), int(p["top"]), int(p["intermediate"])
+        if not 0 < self.top <= self.experts:
+            raise ValueError(f"{self.top} of {self.experts} experts per token")
+        names = dict(expert="experts.{i}.", gate="gate_proj.weight", up="up_proj.weight", down="down_proj.weight",
+                     table="table", shared="shared.")
+        names.update(p.get("names") or {})
+        self.names = names
+        shared = p.get("shared")
+        self.shared = build_part("ffn", shared, ctx) if shared is not None else None
+        self.PROMPT_CAPTURABLE = self.shared is None or bool(self.shared.PROMPT_CAPTURABLE)
+        self.gate_up: Optional[torch.Tensor] = None      # [experts, 2, intermediate, width]
+        self.down: Optional[torch.Tensor] = None         # [experts, width, intermediate]
+        self.table: Optional[torch.Tensor] = None        # int32 [vocab, top]
+
+    def _expert(self, i: int, which: str) -> str:
+        return self.names["expert"].format(i=i) + self.names[which]
+
+    def tensor_specs(self):
+        f, w = self.intermediate, self.width
+        specs = []
+        for i in range(self.experts):
+            specs += [TensorSpec(self._expert(i, "gate"), (f, w)), TensorSpec(self._expert(i, "up"), (f, w)),
+                      TensorSpec(self._expert(i, "down"), (w, f))]
+        specs.append(TensorSpec(self.names["table"], (self.vocab, self.top), "table", init="distinct_below",
+                                init_arg=self.experts))
+        if self.shared is not None:
+            specs += [TensorSpec(self.names["shared"] + s.name, s.shape, s.role, s.optional, s.init, s.init_arg)
+                      for s in self.shared.tensor_specs()]
+        return specs
+
+    def load(self, fetch):
+        hold = self.ctx.hold
+        self.gate_up = torch.stack([torch.stack([hold(fetch(self._expert(i, "gate")), "matrix"),
+                                                 hold(fetch(self._expert(i, "up")), "matrix")]) for i in range(self.experts)])
+        self.down = torch.stack([hold(fetch(self._expert(i, "down")), "matrix") for i in range(self.experts)])
+        self.table = hold(fetch(self.names["table"]), "table")
+        lo, hi = int(self.table.min()), int(self.table.max())
+        if lo < 0 or hi >= self.experts:
+            raise ValueError(f"the expert table names expert {lo if lo < 0 else hi}; there are {self.experts}")
+        if self.shared is not None:
+            self.shared.load(lambda n: fetch(self.names["shared"] + n))
+
+    def tensor(self, name):
+        for i in range(self.experts):
+            pre = self.names["expert"].format(i=i)
+            if name.startswith(pre):
+                which = name[len(pre):]
+                if which == self.names["gate"]:
+                    return self.gate_up[i, 0]
+                if which == self.names["up"]:
+                    return self.gate_up[i, 1]
+                if which == self.names["down"]:
+                    return self.down[i]
+        if name == self.names["table"]:
+            return self.table
+        if self.shared is not None and name.startswith(self.names["shared"]):
+            return self.shared.tensor(name[len(self.names["shared"]):])
+        return None
+
+    def weight_bytes(self):
+        """What a step of one token reads: its experts and the shared part."""
+        el = self.gate_up.element_size() if self.gate_up is not None else (2 if self.ctx.dtype == torch.bfloat16 else 4)
+        n = self.top * 3 * self.intermediate * self.width * el
+        return n + (self.shared.weight_bytes() if self.shared is not None else 0)
+
+    def forward(self, x, batch):
+        base = None
+        if self.shared is not None:
+            base = self.shared.forward(x, batch)
+            if base.dim() == 2:
+                base = base.unsqueeze(0)
+        hidden = ops.moe_table_up(x, batch.tokens, self.table, self.gate_up)
+        return ops.moe_table_down(hidden, batch.tokens, self.table, self.down, 1.0 / self.top, base).unsqueeze(0)
+
+
+register_part("ffn", "none", NoFeedForward)
+register_part("ffn", "mlp", MLP)
+register_part("ffn", "table_moe", TableMoE)

@@ -5,17 +5,24 @@ Each class takes its sizes and constants from ``params`` and nothing else:
 =============  ======================  ==========================================
 category       kind                    params
 =============  ======================  ==========================================
-norm           ``rms``                 width, eps
+norm           ``rms``                 width, eps, offset (added to the stored
+                                       weight, default 0), tensor (its local
+                                       name, default "weight"), optional
 position       ``rotary_half_split``   head_dim, theta
 position       ``none``                —
 mixer          ``gqa_attention``       width, heads, kv_heads, head_dim,
                                        qk_norm (PartSpec or None),
                                        position (PartSpec), scale (or None)
-ffn            ``gated_mlp``           width, intermediate, activation ("silu")
+ffn            ``gated_mlp``           width, intermediate, activation ("silu"),
+                                       names (gate, up, down -> local names)
 block          ``prenorm_residual``    —
-embedding      ``table``               vocab, width
-head           ``linear``              vocab, width, tied
+block          ``postnorm_residual``   alpha
+embedding      ``table``               vocab, width, tensor
+head           ``linear``              vocab, width, tied, tensor, soft_cap
 =============  ======================  ==========================================
+
+Further mixers and position encodings live in ``parts/attention.py``, further
+feed-forwards in ``parts/feedforward.py``.
 
 Formulas and their place in wick: RMS norm ``src/kernels.rs:343-357``; rotation
 ``src/model.rs:404-414`` with ``inv_freq`` from ``src/config.rs:162-167``;
@@ -38,28 +45,50 @@ from .linear import Linear
 
 # ---------------------------------------------------------------------------
 class RMSNorm(Norm):
+    """x / sqrt(mean(x^2) + eps) * (offset + w).  ``offset`` 1 is the form whose weight is
+    stored as its distance from one; the sum is made once, in float32, when the weight is
+    loaded.  ``optional``: the tensor may be absent; the norm then has no weight and must
+    not be run (its owner asks :attr:`present`)."""
+
     PROMPT_CAPTURABLE = True
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
         self.width = int(params["width"])
         self.eps = float(params["eps"])
-        self.weight: Optional[torch.Tensor] = None
+        self.offset = float(params.get("offset", 0.0))
+        self.name = str(params.get("tensor", "weight"))
+        self.optional = bool(params.get("optional", False))
+        self.stored: Optional[torch.Tensor] = None      # as the checkpoint has it
+        self.weight: Optional[torch.Tensor] = None      # offset + stored: the factor
+
+    @property
+    def present(self) -> bool:
+        return self.weight is not None
 
     def tensor_specs(self):
-        return [TensorSpec("weight", (self.width,), "vector")]
+        return [TensorSpec(self.name, (self.width,), "vector", optional=self.optional,
+                           init="around_zero" if self.offset else "")]
 
     def load(self, fetch):
-        self.weight = self.ctx.hold(fetch("weight"), "vector")
+        w = fetch(self.name)
+        if w is None and self.optional:
+            self.stored = self.weight = None
+            return
+        self.stored = self.ctx.hold(w, "vector")
+        self.weight = self.stored + self.offset if self.offset else self.stored
 
     def tensor(self, name):
-        return self.weight if name == "weight" else None
+        return self.stored if name == self.name else None
 
     def forward(self, x, out_dtype, rows=None):
         return ops.rmsnorm(x, self.weight, self.eps, out_dtype, rows=rows)
 
     def add_forward(self, x, delta, out_dtype, rows=None):
         return ops.rmsnorm(x, self.weight, self.eps, out_dtype, delta=delta, rows=rows)
+
+    def scaled_add_forward(self, x, delta, alpha, out_dtype):
+        return ops.scaled_add_rmsnorm(x, delta, alpha, self.weight, self.eps, out_dtype)
 
     def weight_bytes(self):
         return self.width * 4
@@ -250,25 +279,30 @@ class GatedMLP(FeedForward):
         act = params.get("activation", "silu")
         if act != "silu":
             raise ValueError(f"unsupported activation {act}")
+        names = dict(gate="gate_proj.weight", up="up_proj.weight", down="down_proj.weight")
+        names.update(params.get("names") or {})
+        self.names = names
         self.gate_up = Linear(2 * self.intermediate, self.width, ctx, gated=True)
         self.down = Linear(self.width, self.intermediate, ctx)
 
     def tensor_specs(self):
-        return [TensorSpec("gate_proj.weight", (self.intermediate, self.width)),
-                TensorSpec("up_proj.weight", (self.intermediate, self.width)),
-                TensorSpec("down_proj.weight", (self.width, self.intermediate))]
+        nm = self.names
+        return [TensorSpec(nm["gate"], (self.intermediate, self.width)),
+                TensorSpec(nm["up"], (self.intermediate, self.width)),
+                TensorSpec(nm["down"], (self.width, self.intermediate))]
 
     def load(self, fetch):
-        self.gate_up.load_rows([fetch("gate_proj.weight"), fetch("up_proj.weight")])
-        self.down.load_rows([fetch("down_proj.weight")])
+        nm = self.names
+        self.gate_up.load_rows([fetch(nm["gate"]), fetch(nm["up"])])
+        self.down.load_rows([fetch(nm["down"])])
 
     def tensor(self, name):
-        i = self.intermediate
-        if name == "gate_proj.weight":
+        i, nm = self.intermediate, self.names
+        if name == nm["gate"]:
             return self.gate_up.rows(0, i)
-        if name == "up_proj.weight":
+        if name == nm["up"]:
             return self.gate_up.rows(i, 2 * i)
-        return self.down.rows(0, self.width) if name == "down_proj.weight" else None
+        return self.down.rows(0, self.width) if name == nm["down"] else None
 
     def weight_bytes(self):
         return self.gate_up.weight_bytes() + self.down.weight_bytes()
@@ -291,6 +325,7 @@ class PreNormResidual(Block):
 
     def forward(self, h, batch, cache, write_cache):
         dt = self.ctx.dtype
+        h.act = None                     # (this block changes the stream without keeping a copy)
         if h.pending is not None:
             xn = self.mixer_norm.add_forward(h.x, h.pending, dt)
         else:
@@ -308,6 +343,35 @@ class PreNormResidual(Block):
         return h
 
 
+class PostNormResidual(Block):
+    """x <- norm1(alpha x + mixer(x)); x <- norm2(alpha x + ffn(x)): the sublayers read the
+    stream itself and the norm follows the sum.  The stream stays float32; every norm also
+    writes it in the compute dtype, which is what the next sublayer's matrix products read.
+    A layer whose feed-forward is of kind ``none`` ends after its first half (if its second
+    norm has a weight all the same, that norm is applied to alpha x)."""
+
+    PROMPT_CAPTURABLE = True
+
+    def __init__(self, params, ctx, mixer, mixer_norm, ffn, ffn_norm):
+        super().__init__(params, ctx, mixer, mixer_norm, ffn, ffn_norm)
+        self.alpha = float(params.get("alpha", 1.0))
+
+    def forward(self, h, batch, cache, write_cache):
+        dt = self.ctx.dtype
+        x = h.resolved()
+        if h.act is None:
+            h.act = ops.to_activation(x, dt)
+        d = self.mixer.forward(h.act, batch, cache, write_cache)
+        h.act = self.mixer_norm.scaled_add_forward(x, as_splits(d), self.alpha, dt)
+        if getattr(self.ffn, "IS_NONE", False):
+            if getattr(self.ffn_norm, "present", True):
+                h.act = self.ffn_norm.scaled_add_forward(x, None, self.alpha, dt)
+            return h
+        d = self.ffn.forward(h.act, batch)
+        h.act = self.ffn_norm.scaled_add_forward(x, as_splits(d), self.alpha, dt)
+        return h
+
+
 # ---------------------------------------------------------------------------
 class TableEmbedding(Embedding):
     PROMPT_CAPTURABLE = True
@@ -315,16 +379,17 @@ class TableEmbedding(Embedding):
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
         self.vocab, self.width = int(params["vocab"]), int(params["width"])
+        self.name = str(params.get("tensor", "weight"))
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self):
-        return [TensorSpec("weight", (self.vocab, self.width))]
+        return [TensorSpec(self.name, (self.vocab, self.width))]
 
     def load(self, fetch):
-        self.weight = self.ctx.hold(fetch("weight"), "matrix")
+        self.weight = self.ctx.hold(fetch(self.name), "matrix")
 
     def tensor(self, name):
-        return self.weight if name == "weight" else None
+        return self.weight if name in (self.name, "weight") else None
 
     def forward(self, tokens):
         return ops.embed(self.weight, tokens)
@@ -335,7 +400,8 @@ class TableEmbedding(Embedding):
 
 class LinearHead(Head):
     """logits = x W^T in float32.  ``tied``: W is the embedding table.  As in wick
-    (model.rs:190) the head is also tied when its own tensor is absent."""
+    (model.rs:190) the head is also tied when its own tensor is absent.  ``soft_cap`` c:
+    logits <- c tanh(logits / c)."""
 
     PROMPT_CAPTURABLE = True
 
@@ -343,6 +409,9 @@ class LinearHead(Head):
         super().__init__(params, ctx)
         self.vocab, self.width = int(params["vocab"]), int(params["width"])
         self.tied = bool(params.get("tied", False))
+        self.name = str(params.get("tensor", "weight"))
+        cap = params.get("soft_cap")
+        self.soft_cap = float(cap) if cap else None
         self.linear = Linear(self.vocab, self.width, ctx)
         self.is_tied = self.tied
         self.embedding: Optional[Embedding] = None
@@ -353,10 +422,10 @@ class LinearHead(Head):
         self.embedding = peers.get("embedding")
 
     def tensor_specs(self):
-        return [TensorSpec("weight", (self.vocab, self.width), optional=True)]
+        return [TensorSpec(self.name, (self.vocab, self.width), optional=True)]
 
     def load(self, fetch):
-        w = None if self.tied else fetch("weight")
+        w = None if self.tied else fetch(self.name)
         if w is None:
             table = self.embedding.tensor("weight") if self.embedding is not None else None
             if table is None:
@@ -368,10 +437,11 @@ class LinearHead(Head):
             self.is_tied = False
 
     def tensor(self, name):
-        return self.linear.rows(0, self.vocab) if name == "weight" and not self.is_tied else None
+        return self.linear.rows(0, self.vocab) if name == self.name and not self.is_tied else None
 
     def forward(self, x):
-        return self.linear.forward(x, torch.float32)
+        z = self.linear.forward(x, torch.float32)
+        return ops.soft_cap_(z, self.soft_cap) if self.soft_cap is not None else z
 
     def weight_bytes(self):
         return self.linear.weight_bytes()
@@ -383,5 +453,6 @@ register_part("position", "none", NoPosition)
 register_part("mixer", "gqa_attention", GQAttention)
 register_part("ffn", "gated_mlp", GatedMLP)
 register_part("block", "prenorm_residual", PreNormResidual)
+register_part("block", "postnorm_residual", PostNormResidual)
 register_part("embedding", "table", TableEmbedding)
 register_part("head", "linear", LinearHead)

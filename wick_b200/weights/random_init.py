@@ -5,7 +5,8 @@
 any checkpoint.  ``random_fetch`` produces the same kind of tensors directly
 on a device, for sizes that are not worth a round trip through a file.
 
-Matrices are N(0, std) and vectors (norm weights) 1 + N(0, vector_std), each
+Matrices are N(0, std) and vectors (norm weights) 1 + N(0, vector_std), unless a
+tensor's spec names another rule (``TensorSpec.init``), each
 tensor from a generator seeded by (seed, tensor name) so that a tensor's values
 do not depend on which other tensors exist.
 """
@@ -32,9 +33,17 @@ def _make(name: str, ts, seed: int, device, dtype: torch.dtype, std: float, vect
     g = torch.Generator(device=device)
     g.manual_seed(_seed_for(seed, name))
     if ts.role == "table":
-        raise ValueError(f"{name}: no random rule for an integer table")
+        if ts.init != "distinct_below" or len(ts.shape) != 2 or ts.shape[1] > ts.init_arg:
+            raise ValueError(f"{name}: no random rule for this integer table")
+        # every row: the first entries of a random order of 0 .. init_arg - 1
+        keys = torch.rand((ts.shape[0], ts.init_arg), generator=g, device=device)
+        return keys.argsort(dim=1)[:, :ts.shape[1]].to(torch.int32).contiguous()
+    if ts.init == "unit_interval":
+        return (0.2 + 0.6 * torch.rand(ts.shape, generator=g, device=device, dtype=torch.float32)).to(dtype)
     t = torch.randn(ts.shape, generator=g, device=device, dtype=torch.float32)
-    if ts.role == "vector":
+    if ts.init == "around_zero":
+        t = vector_std * t
+    elif ts.role == "vector":
         t = 1.0 + vector_std * t
     else:
         t = std * t
