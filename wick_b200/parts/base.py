@@ -41,7 +41,7 @@ class TensorSpec:
     role's default (matrices N(0, std), vectors 1 + N(0, vector_std)) is none:
     ``around_zero`` (a vector that is added, or a norm weight stored as its distance from
     one), ``unit_interval`` (a blend factor), ``distinct_below`` (integer rows of different
-    values below ``init_arg``)."""
+    values below ``init_arg``), ``absent`` (an optional tensor that random models leave out)."""
 
     name: str
     shape: Tuple[int, ...]

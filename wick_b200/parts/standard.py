@@ -67,8 +67,8 @@ class RMSNorm(Norm):
         return self.weight is not None
 
     def tensor_specs(self):
-        return [TensorSpec(self.name, (self.width,), "vector", optional=self.optional,
-                           init="around_zero" if self.offset else "")]
+        init = "absent" if self.optional else ("around_zero" if self.offset else "")
+        return [TensorSpec(self.name, (self.width,), "vector", optional=self.optional, init=init)]
 
     def load(self, fetch):
         w = fetch(self.name)

@@ -63,7 +63,7 @@ def random_fetch(model: Model, seed: int, *, std: float = 0.02, vector_std: floa
         ts = table.get(name)
         if ts is None:
             return None
-        if ts.optional and getattr(model.head, "tied", False):
+        if ts.optional and (ts.init == "absent" or getattr(model.head, "tied", False)):
             return None
         return _make(name, ts, seed, dev, torch.float32 if ts.role == "vector" else store_dtype, std, vector_std)
 
@@ -77,7 +77,7 @@ def write_random_model(config: ModelConfig, seed: int, out_dir: str, *, dtype: t
     model = Model(arch.build_spec(config), torch.float32, "cpu")
     tensors: Dict[str, torch.Tensor] = {}
     for name, ts in model.tensor_table().items():
-        if ts.optional and getattr(model.head, "tied", False):
+        if ts.optional and (ts.init == "absent" or getattr(model.head, "tied", False)):
             continue
         tensors[name] = _make(name, ts, seed, "cpu", dtype, std, vector_std)
     os.makedirs(out_dir, exist_ok=True)
