@@ -237,6 +237,37 @@ def test_masked_attention_with_a_sink(mask, size, dtype):
         close(out, ref[start:start + n_new], kind, f"{mask} {size}: {n_new} tokens after {start}")
 
 
+@pytest.mark.parametrize("mask,size", [("block", 50), ("block", 64), ("block", 200), ("window", 37), ("causal", 0)])
+@pytest.mark.parametrize("d,H,G", [(16, 4, 4), (48, 6, 2), (128, 2, 1)])
+def test_tensor_core_prompt_attention_equals_the_warp_kernel(mask, size, d, H, G):
+    """Three sequences in one step: from position 0, after a prefix that ends inside a block and a page, and a
+    single row; the tensor-core kernel against the warp kernel on the same cache."""
+    g = torch.Generator().manual_seed(8)
+    lens, starts = [150, 90, 1], [0, 77, 130]
+    pages = [[5, 2, 8], [1, 9, 3], [4, 7, 6]]
+    kv = torch.full((10, 2 * G * PAGE * d), float("nan"))
+    for b in range(3):
+        n = starts[b] + lens[b]
+        k, v = torch.randn(n, G, d, generator=g), torch.randn(n, G, d, generator=g)
+        one = fill_cache(k, v, pages[b], 10)
+        for pg in pages[b][:(n + PAGE - 1) // PAGE]:
+            kv[pg] = one[pg]
+    kv = kv.to(torch.bfloat16).to(DEV)
+    q = torch.randn(sum(lens), H, d, generator=g).to(torch.bfloat16).to(DEV)
+    sink = torch.randn(H, generator=g).to(DEV)
+    lay = BatchLayout(3, sum(lens), 3, 0)
+    host = np.zeros(lay.size, dtype=np.int32)
+    fill_host(lay, host, tokens=[[0] * n for n in lens], starts=starts, slots=[1, 2, 3], pages=pages, want=[[], [], []])
+    batch = StepBatch(lay, torch.from_numpy(host).to(DEV), q_lens=lens, starts=starts)
+    for sk in (sink, None):
+        kw = dict(n_kv=G, v_dim=d, mask=mask, mask_size=size, sink=sk)
+        ref = ops.attention_masked(q, kv, batch, 0.2, kind="warp", **kw)
+        out = ops.attention_masked(q, kv, batch, 0.2, kind="mma", **kw)
+        assert ops.attention_masked_kind(d, d, torch.bfloat16, False) == "mma"
+        assert torch.isfinite(out.float()).all()
+        assert (out.float() - ref.float()).abs().max().item() < 0.03, (mask, size, d, sk is None)
+
+
 @pytest.mark.parametrize("size", [50, 64])
 def test_one_key_that_stands_out_shows_on_which_side_of_an_edge_it_lies(size):
     """Key j is made to dominate every query that sees it (its score is far above all others) and its value is
@@ -399,6 +430,30 @@ def test_pages_and_slots_that_were_given_back_are_used_again(dtype):
     close(torch.stack([r[0] for r in rows]), plain(name, b[:100])[70:], dtype, "the request that stayed")
     close(torch.stack([r[1] for r in rows]), plain(name, a[:130])[100:], dtype, "the request in reused pages")
     eng.cache.check()
+
+
+def test_rows_sorted_by_expert_equal_the_walk_over_tokens():
+    """A step that is launched kernel by kernel sorts its rows by expert and uses the tensor-core products;
+    a captured step walks the tokens.  Same model, same prompt."""
+    from wick_b200.parts.feedforward import TableMoE
+    name = "NC"
+    toks = random_tokens(CONFIGS[name]["vocab"], 300, seed=71)
+    ref = plain(name, toks)
+    calls = []
+    orig = TableMoE._forward_sorted
+    TableMoE._forward_sorted = lambda self, *a: calls.append(1) or orig(self, *a)
+    try:
+        eng = engine(name, "bfloat16", use_graphs=False)
+        s = eng.open_seq()
+        close(eng.step([s], [toks], [list(range(300))]), ref, "bfloat16", "sorted by expert")
+        assert calls, "the step did not sort its rows"
+        n = len(calls)
+        eng2 = engine(name, "float32", use_graphs=False)
+        s = eng2.open_seq()
+        close(eng2.step([s], [toks], [list(range(300))]), ref, "float32", "32-bit walks the tokens")
+        assert len(calls) == n
+    finally:
+        TableMoE._forward_sorted = orig
 
 
 def test_a_far_key_among_hundreds_is_found():

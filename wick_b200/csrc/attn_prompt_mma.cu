@@ -10,6 +10,12 @@
 // m16n8k16 with float32 accumulators; the running maximum, the denominators and
 // the rescaling are float32 in registers.  Scores are multiplied by the scale
 // after the dot product (wick src/model.rs:527,538).
+//
+// Options: a visibility rule beside "every earlier key" (the query's own block of positions,
+// or the last positions: the first page a tile reads is then the one with its first row's first
+// visible key, and keys before a row's first visible one are masked like keys after the row),
+// and a sink per head, a score that joins the denominator without a value (the running maximum
+// starts at the sink, so that its share is at most 1).
 #include "common.cuh"
 
 #ifndef WICK_HD
@@ -58,6 +64,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// First key that the query at position p sees: mask 0 every earlier key, 1 those of p's own block of `size`
+// positions (blocks counted from position 0), 2 the last `size` positions.
+__device__ __forceinline__ int first_visible_key(int p, int mask, int size) {
+    return mask == 1 ? p / size * size : (mask == 2 ? max(0, p - size + 1) : 0);
+}
+
 // One page tile [64][HD] from global (contiguous) into swizzled shared memory.
 __device__ __forceinline__ void load_tile(bf16* dst, const bf16* src, int valid_rows) {
     for (int i = threadIdx.x; i < kPage * CHUNKS; i += 128) {
@@ -70,7 +82,7 @@ __global__ void __launch_bounds__(128)
 attn_prompt_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv, bf16* __restrict__ out,
                        const int* __restrict__ cu_seqlens, int n_seqs, const int* __restrict__ start,
                        const int* __restrict__ page_table, int table_width, int n_tiles, int n_heads, int n_kv,
-                       float scale) {
+                       float scale, int mask, int mask_size, const float* __restrict__ sink) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);              // [64][HD]
     bf16* Ks = Qs + QT * HD;                                   // [2][64][HD]
@@ -92,6 +104,7 @@ attn_prompt_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv, 
     const int kv_len = s0 + q_len;
     const int last_key = s0 + q0 + rows - 1;
     const int n_ktiles = last_key / kPage + 1;
+    const int kt_first = first_visible_key(s0 + q0, mask, mask_size) / kPage;   // (the first visible key grows with the position)
     const int64_t page_elems = (int64_t)2 * n_kv * kPage * HD;
 
     auto tile_ptr = [&](int kt) {
@@ -106,24 +119,27 @@ attn_prompt_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv, 
         cp_async16(Qs + row * HD + swz(row, c) * 8, q + ((int64_t)(tok0 + q0 + src_row) * n_heads + head) * HD + c * 8, true);
     }
     {
-        const bf16* kp = tile_ptr(0);
-        load_tile(Ks, kp, kv_len);
-        load_tile(Vs, kp + (int64_t)n_kv * kPage * HD, kv_len);
+        const bf16* kp = tile_ptr(kt_first);
+        load_tile(Ks + (kt_first & 1) * kPage * HD, kp, kv_len - kt_first * kPage);
+        load_tile(Vs + (kt_first & 1) * kPage * HD, kp + (int64_t)n_kv * kPage * HD, kv_len - kt_first * kPage);
     }
     cp_async_commit();
 
     // per-thread rows: r_lo = 16 warp + lane / 4, r_hi = r_lo + 8
     const int r_lo = warp * 16 + (lane >> 2);
     const int pos_lo = s0 + q0 + min(r_lo, rows - 1), pos_hi = s0 + q0 + min(r_lo + 8, rows - 1);
+    const int vis_lo = first_visible_key(pos_lo, mask, mask_size), vis_hi = first_visible_key(pos_hi, mask, mask_size);
+    const int vis_warp = first_visible_key(s0 + q0 + min(warp * 16 + 15, rows - 1), mask, mask_size);   // the largest of this warp's rows
     const float sl2 = scale * 1.4426950408889634f;              // scores in units of log2(e)
+    const float sink2 = sink ? sink[head] * 1.4426950408889634f : -INFINITY;
 
     uint32_t qf[KS][4];
     float o[ND][4];
 #pragma unroll
     for (int d = 0; d < ND; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
-    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+    float m_lo = sink2, m_hi = sink2, l_lo = 0.f, l_hi = 0.f;
 
-    for (int kt = 0; kt < n_ktiles; ++kt) {
+    for (int kt = kt_first; kt < n_ktiles; ++kt) {
         const int buf = kt & 1;
         if (kt + 1 < n_ktiles) {                                // prefetch the next page into the other buffer
             const bf16* kp = tile_ptr(kt + 1);
@@ -136,7 +152,7 @@ attn_prompt_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv, 
             cp_async_wait<0>();
         }
         __syncthreads();
-        if (kt == 0) {
+        if (kt == kt_first) {
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {
                 const int row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
@@ -163,7 +179,8 @@ attn_prompt_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv, 
         }
         // ---- mask, running maximum, probabilities ----
         const int key0 = kt * kPage + (lane & 3) * 2;
-        const bool need_mask = kt * kPage + kPage - 1 > s0 + q0 + min(warp * 16, rows - 1);   // a key may lie after a row of this warp
+        const bool need_mask = kt * kPage + kPage - 1 > s0 + q0 + min(warp * 16, rows - 1)    // a key may lie after a row of this warp
+                               || kt * kPage < vis_warp;                                      // ... or before a row's first visible key
         float mx_lo = -INFINITY, mx_hi = -INFINITY;
 #pragma unroll
         for (int nb = 0; nb < 8; ++nb) {
@@ -172,8 +189,8 @@ attn_prompt_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv, 
                 const int key = key0 + nb * 8 + e;
                 float a = s[nb][e] * sl2, c = s[nb][2 + e] * sl2;
                 if (need_mask) {
-                    if (key > pos_lo) a = -INFINITY;
-                    if (key > pos_hi) c = -INFINITY;
+                    if (key > pos_lo || key < vis_lo) a = -INFINITY;
+                    if (key > pos_hi || key < vis_hi) c = -INFINITY;
                 }
                 s[nb][e] = a;
                 s[nb][2 + e] = c;
@@ -185,8 +202,11 @@ attn_prompt_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv, 
         mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
         mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
         mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-        const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);   // finite: key 0 is visible to every row
-        const float c_lo = exp2f(m_lo - mn_lo), c_hi = exp2f(m_hi - mn_hi);
+        // (without a mask key 0 is visible to every row and the maxima are finite; with one, a row may see
+        // nothing of the tile's first pages: its maximum stays -inf, and exponents are then taken against 0)
+        const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+        const float rf_lo = mn_lo == -INFINITY ? 0.f : mn_lo, rf_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+        const float c_lo = exp2f(m_lo - rf_lo), c_hi = exp2f(m_hi - rf_hi);
         m_lo = mn_lo;
         m_hi = mn_hi;
         float sum_lo = 0.f, sum_hi = 0.f;
@@ -194,8 +214,8 @@ attn_prompt_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv, 
         for (int nb = 0; nb < 8; ++nb) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                s[nb][e] = exp2f(s[nb][e] - mn_lo);
-                s[nb][2 + e] = exp2f(s[nb][2 + e] - mn_hi);
+                s[nb][e] = exp2f(s[nb][e] - rf_lo);
+                s[nb][2 + e] = exp2f(s[nb][2 + e] - rf_hi);
                 sum_lo += s[nb][e];
                 sum_hi += s[nb][2 + e];
             }
@@ -230,6 +250,10 @@ attn_prompt_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv, 
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    if (sink) {                                                 // (every row sees itself: its maximum is finite by now)
+        l_lo += exp2f(sink2 - m_lo);
+        l_hi += exp2f(sink2 - m_hi);
+    }
     const float i_lo = 1.0f / l_lo, i_hi = 1.0f / l_hi;
     const int col = (lane & 3) * 2;
     if (r_lo < rows) {
@@ -251,11 +275,14 @@ using namespace wick;
 
 WICK_API int wick_attn_prompt_mma_supported() { return promptmma::SUPPORTED ? 1 : 0; }
 
-// Same arguments as wick_attn_prompt_bf16 (attn.cu).
-WICK_API int wick_attn_prompt_mma_bf16(const void* q, const void* kv, void* out, int n_tiles, const int* cu_seqlens,
-                                       int n_seqs, const int* start, const int* page_table,
-                                       int table_width, int n_heads, int n_kv, float scale, void* s) {
+// The arguments of wick_attn_prompt_bf16 (attn.cu), then the mask (0, or 1 / 2 with its size) and the sinks
+// (float32 [n_heads] or null).
+WICK_API int wick_attn_prompt_mma_masked_bf16(const void* q, const void* kv, void* out, int n_tiles, const int* cu_seqlens,
+                                              int n_seqs, const int* start, const int* page_table,
+                                              int table_width, int n_heads, int n_kv, float scale, int mask, int mask_size,
+                                              const float* sink, void* s) {
     using namespace promptmma;
+    WICK_REQUIRE(mask == 0 || ((mask == 1 || mask == 2) && mask_size > 0), "attention: mask %d of size %d", mask, mask_size);
     WICK_REQUIRE(SUPPORTED, "attention (tensor cores): head_dim %d is beyond 128", HD);
     WICK_REQUIRE(n_heads > 0 && n_kv > 0 && n_heads % n_kv == 0, "attention: %d heads over %d kv heads", n_heads, n_kv);
     WICK_REQUIRE(n_heads <= 65535, "attention: %d heads is beyond the grid limit", n_heads);
@@ -268,6 +295,14 @@ WICK_API int wick_attn_prompt_mma_bf16(const void* q, const void* kv, void* out,
     }
     WICK_CUDA(launch(attn_prompt_mma_kernel, dim3(n_tiles, n_heads), dim3(128), smem, (cudaStream_t)s, (const bf16*)q,
                      (const bf16*)kv, (bf16*)out, cu_seqlens, n_seqs, start, page_table, table_width, n_tiles,
-                     n_heads, n_kv, scale));
+                     n_heads, n_kv, scale, mask, mask_size, sink));
     return check_launch("attn_prompt_mma");
+}
+
+// Same arguments as wick_attn_prompt_bf16 (attn.cu).
+WICK_API int wick_attn_prompt_mma_bf16(const void* q, const void* kv, void* out, int n_tiles, const int* cu_seqlens,
+                                       int n_seqs, const int* start, const int* page_table,
+                                       int table_width, int n_heads, int n_kv, float scale, void* s) {
+    return wick_attn_prompt_mma_masked_bf16(q, kv, out, n_tiles, cu_seqlens, n_seqs, start, page_table, table_width, n_heads,
+                                            n_kv, scale, 0, 0, nullptr, s);
 }

@@ -87,6 +87,86 @@ moe_down_kernel(const T* __restrict__ hidden, const int* __restrict__ tokens, co
     }
 }
 
+// ---- the form for many tokens: rows sorted by expert ---------------------------------------
+// The (token, choice) pairs of a step, numbered t * top + c, are sorted by expert (pairs of one
+// expert keep their order), so that every expert's rows lie together and go through an ordinary
+// matrix product.  route: expert_of[pair] and counts[expert]; place: row_of[pair] (a warp per
+// expert walks all pairs in order and numbers its own); gather: the sorted rows of x; combine:
+// out[t] = base[t] + weight * (y[row_of[t, 0]] + y[row_of[t, 1]] + ...), choices in table order.
+__global__ void moe_route_kernel(const int* __restrict__ tokens, const int* __restrict__ table, int top, int n_experts,
+                                 int* __restrict__ expert_of, int* __restrict__ counts, int n_pairs) {
+    pdl_trigger();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_pairs) return;
+    const int t = i / top, c = i - t * top;
+    int ex = table[(int64_t)tokens[t] * top + c];
+    if (ex < 0 || ex >= n_experts) ex = -1;
+    expert_of[i] = ex;
+    if (ex >= 0) atomicAdd(counts + ex, 1);               // (a count: the order of the additions does not matter)
+}
+
+__global__ void __launch_bounds__(32)
+moe_place_kernel(const int* __restrict__ expert_of, const int* __restrict__ counts, int* __restrict__ row_of, int n_pairs) {
+    pdl_trigger();
+    pdl_wait();
+    expert_of = fresh(expert_of);
+    counts = fresh(counts);
+    const int ex = blockIdx.x, lane = threadIdx.x;
+    int base = 0;
+    for (int e = 0; e < ex; ++e) base += counts[e];
+    for (int i0 = 0; i0 < n_pairs; i0 += 32) {
+        const int i = i0 + lane;
+        const bool mine = i < n_pairs && expert_of[i] == ex;
+        const unsigned m = __ballot_sync(0xffffffffu, mine);
+        if (mine) row_of[i] = base + __popc(m & ((1u << lane) - 1));
+        base += __popc(m);
+    }
+    if (ex == 0)                                           // pairs without an expert have no row
+        for (int i = lane; i < n_pairs; i += 32)
+            if (expert_of[i] < 0) row_of[i] = -1;
+}
+
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ row_of, int top, T* __restrict__ xs, int width) {
+    pdl_trigger();
+    pdl_wait();
+    x = fresh(x);
+    row_of = fresh(row_of);
+    const int pair = blockIdx.x, row = row_of[pair];
+    if (row < 0) return;
+    const T* src = x + (int64_t)(pair / top) * width;
+    T* dst = xs + (int64_t)row * width;
+    constexpr int VN = Vec16<T>::N;
+    if (width % VN == 0 && (((uintptr_t)x | (uintptr_t)xs) & 15) == 0) {
+        for (int j = threadIdx.x * VN; j < width; j += blockDim.x * VN)
+            *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(src + j);
+    } else {
+        for (int j = threadIdx.x; j < width; j += blockDim.x) dst[j] = src[j];
+    }
+}
+
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ row_of, int top, float weight,
+                                   const float* __restrict__ base, int base_splits, int64_t base_stride,
+                                   float* __restrict__ out, int width) {
+    pdl_trigger();
+    pdl_wait();
+    y = fresh(y);
+    row_of = fresh(row_of);
+    base = fresh(base);
+    const int t = blockIdx.x;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        float sum = 0.f;
+        for (int c = 0; c < top; ++c) {
+            const int row = row_of[t * top + c];
+            if (row >= 0) sum += y[(int64_t)row * width + j];
+        }
+        float v = 0.f;
+        for (int s = 0; s < base_splits; ++s) v += base[s * base_stride + (int64_t)t * width + j];
+        out[(int64_t)t * width + j] = v + weight * sum;
+    }
+}
+
 template <typename T>
 int moe_up(const void* x, const int* tokens, const int* table, int top, int n_experts, const void* gate_up, void* hidden, int n,
            int width, int ff, cudaStream_t s) {
@@ -134,4 +214,34 @@ WICK_API int wick_moe_down_f32(const void* hidden, const int* tokens, const int*
                                float weight, const float* base, int base_splits, float* out, int n, int width, int ff, void* s) {
     return moe_down<float>(hidden, tokens, table, top, n_experts, down, weight, base, base_splits, out, n, width, ff,
                            (cudaStream_t)s);
+}
+
+// expert_of, row_of: int32 [n * top]; counts: int32 [experts], zero on entry.
+WICK_API int wick_moe_route(const int* tokens, const int* table, int top, int n_experts, int* expert_of, int* counts,
+                            int* row_of, int n, void* s) {
+    WICK_REQUIRE(top > 0 && n_experts > 0 && n >= 0, "moe_route: bad sizes");
+    if (n == 0) return 0;
+    const int pairs = n * top;
+    WICK_CUDA(launch(moe_route_kernel, dim3(ceil_div(pairs, 256)), dim3(256), 0, (cudaStream_t)s, tokens, table, top, n_experts,
+                     expert_of, counts, pairs));
+    WICK_CUDA(launch(moe_place_kernel, dim3(n_experts), dim3(32), 0, (cudaStream_t)s, (const int*)expert_of, (const int*)counts,
+                     row_of, pairs));
+    return check_launch("moe_route");
+}
+WICK_API int wick_moe_gather_bf16(const void* x, const int* row_of, int top, void* xs, int n, int width, void* s) {
+    if (n == 0) return 0;
+    WICK_CUDA(launch(moe_gather_kernel<bf16>, dim3(n * top), dim3(128), 0, (cudaStream_t)s, (const bf16*)x, row_of, top, (bf16*)xs, width));
+    return check_launch("moe_gather");
+}
+WICK_API int wick_moe_gather_f32(const void* x, const int* row_of, int top, void* xs, int n, int width, void* s) {
+    if (n == 0) return 0;
+    WICK_CUDA(launch(moe_gather_kernel<float>, dim3(n * top), dim3(128), 0, (cudaStream_t)s, (const float*)x, row_of, top, (float*)xs, width));
+    return check_launch("moe_gather");
+}
+WICK_API int wick_moe_combine(const float* y, const int* row_of, int top, float weight, const float* base, int base_splits,
+                              float* out, int n, int width, void* s) {
+    if (n == 0) return 0;
+    WICK_CUDA(launch(moe_combine_kernel, dim3(n), dim3(256), 0, (cudaStream_t)s, y, row_of, top, weight, base, base_splits,
+                     (int64_t)n * width, out, width));
+    return check_launch("moe_combine");
 }

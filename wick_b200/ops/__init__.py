@@ -633,14 +633,26 @@ def qkv_finish(parts: torch.Tensor, n_heads: int, n_kv: int, d: int, e: int, *, 
     return q_out
 
 
+def attention_masked_kind(d: int, v_dim: int, dtype: torch.dtype, is_decode: bool, plain: bool = False) -> str:
+    """Which kernel :func:`attention_masked` runs: ``mma`` (tensor cores through mma.sync: a
+    prompt's tokens in bfloat16 with keys and values of one size, a multiple of 16 up to 128)
+    or ``warp`` (CUDA cores, a warp per token and head: everything else, and the twin that the
+    former is checked against)."""
+    if plain or PLAIN_KERNELS or is_decode or dtype != torch.bfloat16 or d != v_dim or d % 16 != 0 or d > 128:
+        return "warp"
+    return "mma"
+
+
 def attention_masked(q: torch.Tensor, kv: torch.Tensor, batch, scale: float, *, n_kv: int, v_dim: int,
-                     mask: str = "causal", mask_size: int = 0, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     mask: str = "causal", mask_size: int = 0, sink: Optional[torch.Tensor] = None,
+                     kind: Optional[str] = None) -> torch.Tensor:
     """Attention of the step's tokens (a prompt's or one per sequence) over the cache, which
     already holds their keys and values.  q: [n, H, d]; result [n, H, v_dim].  ``mask``:
     ``causal`` (every earlier key), ``block`` (earlier keys in the query's own block of
     ``mask_size`` positions, blocks counted from position 0) or ``window`` (the last
     ``mask_size`` positions).  ``sink``: float32 [H], a score per head that joins the
-    softmax's denominator without a value."""
+    softmax's denominator without a value.  ``kind`` picks a kernel by hand (see
+    :func:`attention_masked_kind`)."""
     _cuda("q", q)
     n, n_heads, d = q.shape
     _kv_pages("kv", kv, q.dtype, n_kv, d, v_dim)
@@ -648,6 +660,13 @@ def attention_masked(q: torch.Tensor, kv: torch.Tensor, batch, scale: float, *, 
     if sink is not None:
         _cuda("sink", sink, torch.float32, (n_heads,))
     out = torch.empty((n, n_heads, v_dim), dtype=q.dtype, device=q.device)
+    kind = kind or attention_masked_kind(d, v_dim, q.dtype, batch.is_decode)
+    if kind == "mma":
+        _need(q.dtype == torch.bfloat16 and d == v_dim, "the tensor-core kernel takes bfloat16 and one head size")
+        _attn(d).call("wick_attn_prompt_mma_masked_bf16", "pppipippiiifiipp", _p(q), _p(kv), _p(out), attention_tiles(batch),
+                      _p(batch.cu_seqlens), batch.n_seqs, _p(batch.start), _p(batch.page_table), batch.table_width, n_heads,
+                      n_kv, float(scale), MASKS[mask], int(mask_size), _p(sink), _stream())
+        return out
     _layer().call(f"wick_attn_masked_{_dt(q)}", "ppppppiiiiiifiipp", _p(q), _p(kv), _p(out), _p(batch.seq_of_token),
                   _p(batch.positions), _p(batch.page_table), batch.table_width, n, n_heads, n_kv, d, v_dim, float(scale),
                   MASKS[mask], int(mask_size), _p(sink), _stream())
@@ -690,6 +709,50 @@ def moe_table_down(hidden: torch.Tensor, tokens: torch.Tensor, table: torch.Tens
     out = torch.empty((n, width), dtype=torch.float32, device=hidden.device)
     _layer().call(f"wick_moe_down_{_dt(hidden)}", "pppiipfpipiiip", _p(hidden), _p(tokens), _p(table), top, down.shape[0],
                   _p(down), float(weight), _p(base), splits, _p(out), n, width, ff, _stream())
+    return out
+
+
+def moe_route(tokens: torch.Tensor, table: torch.Tensor, n_experts: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The step's (token, choice) pairs sorted by expert: (counts int32 [experts], row_of int32
+    [n, top]): pair (t, c) is row ``row_of[t, c]`` of the sorted order, in which expert 0's pairs
+    come first and pairs of one expert keep their order (-1: the table names no expert)."""
+    n = tokens.numel()
+    _cuda("tokens", tokens, torch.int32, (n,))
+    _cuda("table", table, torch.int32)
+    top = table.shape[1]
+    counts = torch.zeros(n_experts, dtype=torch.int32, device=tokens.device)
+    expert_of = torch.empty((n, top), dtype=torch.int32, device=tokens.device)
+    row_of = torch.empty((n, top), dtype=torch.int32, device=tokens.device)
+    _layer().call("wick_moe_route", "ppiipppip", _p(tokens), _p(table), top, n_experts, _p(expert_of), _p(counts), _p(row_of),
+                  n, _stream(), kernels=2)
+    return counts, row_of
+
+
+def moe_gather(x: torch.Tensor, row_of: torch.Tensor, n_rows: int) -> torch.Tensor:
+    """xs[row_of[t, c]] = x[t]: the rows of x in the sorted order, [n_rows, width]."""
+    _cuda("x", x)
+    n, width = x.shape
+    _cuda("row_of", row_of, torch.int32)
+    top = row_of.shape[1]
+    xs = torch.empty((n_rows, width), dtype=x.dtype, device=x.device)
+    _layer().call(f"wick_moe_gather_{_dt(x)}", "ppipiip", _p(x), _p(row_of), top, _p(xs), n, width, _stream())
+    return xs
+
+
+def moe_combine(y: torch.Tensor, row_of: torch.Tensor, weight: float, base: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """float32 out[t] = sum(base[:, t]) + weight * sum over c of y[row_of[t, c]]."""
+    _cuda("y", y, torch.float32)
+    _cuda("row_of", row_of, torch.int32)
+    n, top = row_of.shape
+    width = y.shape[1]
+    splits = 0
+    if base is not None:
+        _cuda("base", base, torch.float32)
+        _need(base.dim() == 3 and tuple(base.shape[1:]) == (n, width), f"base must be [splits, {n}, {width}]")
+        splits = base.shape[0]
+    out = torch.empty((n, width), dtype=torch.float32, device=y.device)
+    _layer().call("wick_moe_combine", "ppifpipiip", _p(y), _p(row_of), top, float(weight), _p(base), splits, _p(out), n, width,
+                  _stream())
     return out
 
 

@@ -22,7 +22,7 @@ the shared part's.
 """
 from __future__ import annotations
 
-from typing import Optional
+from typing import List, Optional
 
 import torch
 
@@ -97,6 +97,9 @@ class TableMoE(FeedForward):
         self.gate_up: Optional[torch.Tensor] = None      # [experts, 2, intermediate, width]
         self.down: Optional[torch.Tensor] = None         # [experts, width, intermediate]
         self.table: Optional[torch.Tensor] = None        # int32 [vocab, top]
+        # The same matrices once more, one tensor-core plan per expert, for steps of many tokens (bfloat16).
+        self.expert_up: List[Linear] = []
+        self.expert_down: List[Linear] = []
 
     def _expert(self, i: int, which: str) -> str:
         return self.names["expert"].format(i=i) + self.names[which]
@@ -125,6 +128,18 @@ class TableMoE(FeedForward):
             raise ValueError(f"the expert table names expert {lo if lo < 0 else hi}; there are {self.experts}")
         if self.shared is not None:
             self.shared.load(lambda n: fetch(self.names["shared"] + n))
+        self.expert_up, self.expert_down = [], []
+        if self.ctx.dtype == torch.bfloat16 and self.gate_up.is_cuda and not ops.plain_kernels():
+            for i in range(self.experts):
+                up = Linear(2 * self.intermediate, self.width, self.ctx, gated=True)
+                up.use(self.gate_up[i].reshape(2 * self.intermediate, self.width))
+                down = Linear(self.width, self.intermediate, self.ctx)
+                down.use(self.down[i])
+                if up._tensor_core() is None or down._tensor_core() is None:
+                    self.expert_up, self.expert_down = [], []
+                    break
+                self.expert_up.append(up)
+                self.expert_down.append(down)
 
     def tensor(self, name):
         for i in range(self.experts):
@@ -155,8 +170,32 @@ class TableMoE(FeedForward):
             base = self.shared.forward(x, batch)
             if base.dim() == 2:
                 base = base.unsqueeze(0)
+        n = x.shape[0]
+        if self.expert_up and n >= self.SORTED_FROM and not torch.cuda.is_current_stream_capturing():
+            return self._forward_sorted(x, batch, base)
         hidden = ops.moe_table_up(x, batch.tokens, self.table, self.gate_up)
         return ops.moe_table_down(hidden, batch.tokens, self.table, self.down, 1.0 / self.top, base).unsqueeze(0)
+
+    # From this many tokens on a step (that is not being captured) sorts its rows by expert and
+    # runs every expert's rows through the tensor-core products; the host reads the experts' row
+    # counts for that (one wait per layer).  Fewer tokens walk their experts' matrices one by one.
+    SORTED_FROM = 64
+
+    def _forward_sorted(self, x, batch, base):
+        n, dt = x.shape[0], self.ctx.dtype
+        counts, row_of = ops.moe_route(batch.tokens, self.table, self.experts)
+        counts = counts.tolist()                            # (the host waits here)
+        rows = sum(counts)
+        xs = ops.moe_gather(x, row_of, rows)
+        hidden = torch.empty((rows, self.intermediate), dtype=dt, device=x.device)
+        y = torch.empty((rows, self.width), dtype=torch.float32, device=x.device)
+        at = 0
+        for i, c in enumerate(counts):
+            if c:
+                self.expert_up[i]._tensor_core()._run(xs[at:at + c], hidden[at:at + c], 1)
+                self.expert_down[i]._tensor_core()._run(hidden[at:at + c], y[at:at + c], 1)
+                at += c
+        return ops.moe_combine(y, row_of, 1.0 / self.top, base).unsqueeze(0)
 
 
 register_part("ffn", "none", NoFeedForward)
