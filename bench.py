@@ -2,6 +2,7 @@
 """Decode and prefill throughput of wick_b200 on one B200, as one JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--model 8b|14b|32b]
+    python bench.py --design nibotar [--design-size 2k|4k]      (a line of its own, see below)
 
 The default run has the layer sizes of Qwen3-8B (36 layers, hidden 4096, 32
 heads over 8 kv heads of 128, intermediate 12288, vocabulary 151936) with random
@@ -21,6 +22,15 @@ prompts of 64 to 2,048 tokens) and Qwen3-32B sizes (batch 8, 1,024-token prompts
 each with its fraction of the copy bandwidth.  Every weight matrix is far larger
 than the L2 cache, so consecutive steps never find their inputs there.  The run
 fails if any step it timed produced logits that are not finite.
+
+``--design nibotar`` leaves the default workload alone and prints another line: prefill
+(one 2,048-token prompt) and decode (batch 8 and 64, 512-token prompts) throughput of the
+Nibotar design at layer sizes that resemble a real model's (random weights), beside Qwen3
+at equal size (same width, heads, layers and vocabulary; its intermediate size is what a
+Nibotar token's experts and shared expert add up to), and ``parts``: where a prompt step and
+a decode step of each spend their time, per kind of kernel, with the fraction of the
+measured peak each reaches (a second process times them with CUDA events around every call,
+launched one by one without programmatic dependent launch, so that they do not overlap).
 """
 import argparse
 import json
@@ -214,6 +224,193 @@ def other_model(torch, wick, pk, name, steps, warmup, layers=None):
     return out
 
 
+# Layer sizes for --design: Nibotar (one dense layer, then layers of experts) and Qwen3 at equal size.
+DESIGN_SIZES = {
+    "2k": dict(width=2048, heads=16, kv=4, dim=128, layers=8, vocab=32768, mask=1024, dense_ff=8192, experts=8, top=2,
+               expert_ff=1536, shared_ff=2048),
+    "4k": dict(width=4096, heads=32, kv=8, dim=128, layers=4, vocab=32768, mask=2048, dense_ff=16384, experts=16, top=2,
+               expert_ff=2048, shared_ff=4096),
+}
+
+
+def design_configs(z):
+    mixer = dict(heads=z["heads"], kv_heads=z["kv"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5, v_mix=True,
+                 mask={"size": z["mask"]}, rot={"dims": z["dim"], "base": 500000.0})
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]},
+           "shared": {"ff": z["shared_ff"]}}
+    layers = [dict(type="attention", mixer=mixer, mlp={"kind": "dense", "ff": z["dense_ff"]} if i == 0 else moe)
+              for i in range(z["layers"])]
+    nib = dict(architecture="Nibotar", vocab=z["vocab"], width=z["width"], norm={"eps": 1e-5}, postln_alpha=2.0,
+               logit_softcap=30.0, layers=layers)
+    qwen = _qwen3(z["width"], z["heads"], z["kv"], z["top"] * z["expert_ff"] + z["shared_ff"], z["layers"])
+    qwen.update(head_dim=z["dim"], vocab_size=z["vocab"])
+    return {"nibotar": nib, "qwen3": qwen}
+
+
+def design_step_bytes(eng, z, name, batch, kv_tokens):
+    """Bytes a decode step has to read: every weight it uses once, plus the cache it reads.  Of a layer's experts a
+    batch uses E (1 - (1 - top / E)^batch) on average; a block mask reads at most one block of positions."""
+    n = eng.model.weight_bytes_per_step()
+    if name == "nibotar":
+        e, top = z["experts"], z["top"]
+        one = 3 * z["expert_ff"] * z["width"] * 2
+        used = e * (1.0 - (1.0 - top / e) ** batch)
+        n += (z["layers"] - 1) * (used - top) * one
+        kv_tokens = min(kv_tokens, batch * z["mask"])
+    return n + eng.cache.read_bytes(int(kv_tokens), batch)
+
+
+def design_model(torch, wick, pk, z, name, cfg_json, steps, warmup):
+    cfg = wick.config_from_json(cfg_json)
+    per_seq = (PROMPT + warmup + REPEATS * steps + 2 + 64 + 63) // 64 * 64
+    eng = wick.Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=max(64 * per_seq, PREFILL + 64))
+    out = {}
+    ptoks = random_prompts(torch, z["vocab"], [PREFILL], 3)[0]
+    times = []
+    for i in range(3 + 10):
+        s = eng.open_seq()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        logits = eng.step([s], [ptoks])
+        e1.record()
+        torch.cuda.synchronize()
+        eng.close_seq(s)
+        if i >= 3:
+            times.append(e0.elapsed_time(e1))
+    ok = bool(torch.isfinite(logits).all().item())
+    pms = statistics.median(times)
+    out["prefill"] = {"tokens": PREFILL, "ms": pms, "tok_s": PREFILL / (pms * 1e-3)}
+    for b in (8, 64):
+        regions, launches, kv_tokens, _, finite = device_timed_decode(
+            torch, wick, eng, random_prompts(torch, z["vocab"], [PROMPT] * b, 10 + b), steps, warmup)
+        ms = statistics.median(regions)
+        nbytes = design_step_bytes(eng, z, name, b, kv_tokens)
+        out[f"decode_b{b}"] = {"tok_s": b * 1e3 / ms, "ms_per_step": ms, "gb_per_step": nbytes / 1e9,
+                               "hbm_frac": nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], "launches": launches}
+        ok = ok and finite
+    out["finite"] = ok
+    del eng
+    torch.cuda.empty_cache()
+    return out
+
+
+def design_parts(torch, wick, pk, z, name, cfg_json):
+    """Microseconds per layer that a 2,048-token prompt step and a decode step of 8 sequences (1,500 cached positions
+    each) spend in each kind of kernel, with what each reaches of the measured peak."""
+    from wick_b200 import ops
+    cfg = wick.config_from_json(cfg_json)
+    eng = wick.Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=8 * 1600 + PREFILL + 64, use_graphs=False)
+    acc = {}
+
+    def timed(kind, fn):
+        def run(*a, **kw):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(torch.cuda.current_stream())
+            r = fn(*a, **kw)
+            e1.record(torch.cuda.current_stream())
+            acc.setdefault(kind, []).append((e0, e1))
+            return r
+        return run
+
+    for fname, kind in (("attention_masked", "attention"), ("attention_prompt", "attention"),
+                        ("attention_decode_parts_fused", "attention+finish"), ("attention_decode", "attention"),
+                        ("qkv_finish", "finish"), ("qk_norm_rope_append", "finish"), ("scaled_add_rmsnorm", "norm"),
+                        ("rmsnorm", "norm")):
+        setattr(ops, fname, timed(kind, getattr(ops, fname)))       # (the parts call these through the module)
+    for blk in eng.model.blocks:
+        blk.ffn.forward = timed("ffn " + type(blk.ffn).__name__, blk.ffn.forward)
+        m = blk.mixer
+        m.qkv.forward_delta = timed("qkv product", m.qkv.forward_delta)
+        m.o.forward_delta = timed("o product", m.o.forward_delta)
+    L, D, H, G, d = z["layers"], z["width"], z["heads"], z["kv"], z["dim"]
+    act_ff = z["top"] * z["expert_ff"] + z["shared_ff"]
+
+    def collect(n_tok, kv_read_tokens, att_pairs):
+        torch.cuda.synchronize()
+        res = {}
+        for kind, evs in acc.items():
+            res[kind] = {"us_per_layer": sum(a.elapsed_time(b) for a, b in evs) * 1e3 / L}
+        acc.clear()
+        qkv_w, o_w = D * (H + 2 * G) * d, D * H * d
+        for kind, r in res.items():
+            t = r["us_per_layer"] * 1e-6
+            if kind in ("qkv product", "o product"):
+                w = qkv_w if kind[0] == "q" else o_w
+                r["tflops"], r["gbs"] = 2.0 * n_tok * w / t / 1e12, 2.0 * w / t / 1e9
+            elif kind.startswith("ffn"):
+                if "MLP" in kind and "Gated" not in kind:
+                    w = 2 * D * z["dense_ff"]
+                    r["us_per_layer"] *= L                     # (one such layer)
+                    t *= L
+                elif "TableMoE" in kind:
+                    w = 3 * D * act_ff
+                    r["us_per_layer"] *= L / (L - 1.0)
+                    t *= L / (L - 1.0)
+                else:
+                    w = 3 * D * act_ff
+                r["tflops"] = 2.0 * n_tok * w / t / 1e12
+            elif kind.startswith("attention"):
+                r["tflops"] = 4.0 * H * d * att_pairs / t / 1e12
+                r["gbs"] = kv_read_tokens * 2 * G * d * 2 / t / 1e9
+            elif kind == "norm":
+                r["gbs"] = n_tok * D * (4 + 4 + 4 + 2) / (t / 2) / 1e9      # two norms a layer; stream in, sums in, stream out, copy out
+            elif kind == "finish":
+                r["gbs"] = n_tok * (H + 2 * G) * d * (4 + 2) / t / 1e9
+            for k, peak in (("tflops", pk["bf16_tflops"]), ("gbs", pk["hbm_gbs"])):
+                if k in r:
+                    r[k + "_frac"] = r[k] / peak
+        return res
+
+    out = {}
+    ptoks = random_prompts(torch, z["vocab"], [PREFILL], 3)[0]
+    for i in range(3):
+        s = eng.open_seq()
+        acc.clear()
+        eng.step([s], [ptoks])
+        eng.close_seq(s)
+    n = PREFILL
+    blk = z["mask"] if name == "nibotar" else None
+    pairs = sum((p % blk if blk else p) + 1 for p in range(n))
+    out["prompt_2048"] = collect(n, n, pairs)
+    slots = [eng.open_seq() for _ in range(8)]
+    ctx = random_prompts(torch, z["vocab"], [1500] * 8, 4)
+    eng.step(slots, ctx)
+    for i in range(4):
+        acc.clear()
+        eng.step(slots, [[1 + i]] * 8)
+    seen = (min(1504, 1504 % blk + 1) if blk else 1504)
+    out["decode_b8_ctx1500"] = collect(8, 8 * seen, 8 * seen)
+    return out
+
+
+def design_compare(args) -> int:
+    import torch
+    import wick_b200 as wick
+    pk = peaks()
+    z = DESIGN_SIZES[args.design_size]
+    cfgs = design_configs(z)
+    if args.design_parts:
+        print(json.dumps({name: design_parts(torch, wick, pk, z, name, cfgs[name]) for name in ("nibotar", "qwen3")}))
+        return 0
+    steps, warmup = min(args.steps, 64), max(args.warmup, 3)
+    with Clocks() as clk:
+        models = {name: design_model(torch, wick, pk, z, name, cfgs[name], steps, warmup) for name in ("nibotar", "qwen3")}
+    env = dict(os.environ, WICK_B200_NO_PDL="1")
+    r = subprocess.run([sys.executable, os.path.abspath(__file__), "--design", args.design, "--design-size", args.design_size,
+                        "--design-parts"], env=env, capture_output=True, text=True)
+    parts = None
+    for ln in r.stdout.splitlines():
+        if ln.startswith("{"):
+            parts = json.loads(ln)
+    line = {"metric": f"Nibotar beside Qwen3 at equal size ({args.design_size}): prefill and decode tok/s, bf16", "unit": "tokens/s",
+            "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16", "sizes": z,
+            "data": "synthetic: seeded random weights, seeded uniform random token ids", "models": models, "parts": parts,
+            "parts_error": None if parts is not None else r.stderr[-600:], "clocks": clk.result, "peaks": pk}
+    print(json.dumps(line))
+    return 0 if all(m["finite"] for m in models.values()) else 1
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -234,9 +431,14 @@ def main() -> int:
     ap.add_argument("--skip-prefill", action="store_true")
     ap.add_argument("--skip-decode", action="store_true", help="prefill only (for profiling)")
     ap.add_argument("--eager", action="store_true", help="no CUDA graphs (every kernel is a launch of its own)")
+    ap.add_argument("--design", default=None, choices=["nibotar"], help="another line: this design beside Qwen3 at equal size")
+    ap.add_argument("--design-size", default="2k", choices=sorted(DESIGN_SIZES))
+    ap.add_argument("--design-parts", action="store_true", help="only the per-kernel times of --design (run by --design itself)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
+    if args.design:
+        return design_compare(args)
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not built")
         return 2

@@ -7,11 +7,11 @@
 //
 //   finish  : the q/k/v projection's float32 partial sums -> q (activation type) and the
 //             token's key and value in its sequence's cache page
-//   attend  : every new token over the cache, one warp per (token, query head)
+//   attend  : every new token over the cache, one block per (token, query head)
 //
 // Cache page of one schedule entry: [kv_head][64][d] keys, then [kv_head][64][e] values.
 // Scores, the softmax, its weights and the weighted sum are float32.  A token's work is the
-// same whatever else the step holds: keys are walked 32 at a time from the first visible one.
+// same whatever else the step holds, up to the number of warps that share its keys.
 #include "common.cuh"
 
 namespace wick {
@@ -47,11 +47,34 @@ qkv_finish_kernel(const float* __restrict__ parts, int splits, int64_t split_str
     v_keep = fresh(v_keep);
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
     const int Wq = H * d, Wk = G * d, Wv = G * e, W = Wq + Wk + Wv;
-    for (int j = tid; j < W; j += blockDim.x) {
-        float v = parts[(int64_t)t * W + j];
-        for (int s = 1; s < splits; ++s) v += parts[s * split_stride + (int64_t)t * W + j];
-        if (bias) v += bias[j];
-        row[j] = v;
+    if ((W & 3) == 0 && (split_stride & 3) == 0) {
+        // four neighbours a load, the loads of four partial sums issued together (a chain of dependent trips to
+        // the L2 cache is what a step of few tokens would otherwise wait for); the sums in index order
+        for (int j = tid * 4; j < W; j += blockDim.x * 4) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s0 = 0; s0 < splits; s0 += 4) {
+                float4 p4[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    p4[u] = s0 + u < splits ? *reinterpret_cast<const float4*>(parts + (s0 + u) * split_stride + (int64_t)t * W + j)
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    v.x += p4[u].x; v.y += p4[u].y; v.z += p4[u].z; v.w += p4[u].w;
+                }
+            }
+            if (bias) {
+                v.x += bias[j]; v.y += bias[j + 1]; v.z += bias[j + 2]; v.w += bias[j + 3];
+            }
+            *reinterpret_cast<float4*>(row + j) = v;
+        }
+    } else {
+        for (int j = tid; j < W; j += blockDim.x) {
+            float v = parts[(int64_t)t * W + j];
+            for (int s = 1; s < splits; ++s) v += parts[s * split_stride + (int64_t)t * W + j];
+            if (bias) v += bias[j];
+            row[j] = v;
+        }
     }
     __syncthreads();
     const int nq = q_w ? Wq / q_span : 0, nk = k_w ? Wk / k_span : 0;
@@ -106,74 +129,137 @@ qkv_finish_kernel(const float* __restrict__ parts, int splits, int64_t split_str
 }
 
 // ---------------------------------------------------------------------------
-// One warp per (token, query head).  32 keys at a time: lane l scores key j0 + l (a dot
-// product of d numbers, in index order), the running maximum and sum follow, then every
-// lane adds the 32 weighted value rows into its elements l, l + 32, ... of the result.
-// A sink starts the running maximum at its value and the sum at 1: a key with that score
-// and no value.
-constexpr int E_PER_LANE = 8;                  // value sizes up to 256
+// One block per (token, query head); its warps share the visible keys, 32 at a time: warp w
+// takes the keys lo + 32 w .., lo + 32 (w + warps) .., and so on.  In a tile, lane l scores key
+// j0 + l (a dot product of d numbers, in index order), the warp's running maximum and sum
+// follow, then every lane adds the 32 weighted value rows into its own elements of the result.
+// At the end the warps' partial results are folded in warp order; a sink joins there as a
+// score without a value.  The number of warps is chosen by the step's size (few tokens: 8,
+// so that a decode step keeps the part busy; many: 1), which changes the order of sums only.
+constexpr int E_CHUNKS = 2;                    // value sizes up to 256: a lane holds 4 neighbours of every 128
+
+__device__ __forceinline__ void load4(const float* p, float* v) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float* v) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.y));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
 
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 attn_masked_kernel(const T* __restrict__ q, const T* __restrict__ kv, T* __restrict__ out,
                    const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                    const int* __restrict__ page_table, int table_width, int n_tokens, int H, int G, int d, int e,
                    float scale, int mask, int mask_size, const float* __restrict__ sink) {
-    extern __shared__ float qs_all[];
+    extern __shared__ float smem[];
     pdl_trigger();
     pdl_wait();
     q = fresh(q);
     kv = fresh(kv);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int64_t id = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
-    if (id >= (int64_t)n_tokens * H) return;
-    const int t = (int)(id / H), h = (int)(id - (int64_t)t * H);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int t = blockIdx.x / H, h = blockIdx.x - t * H;
     const int g = h / (H / G);
     const int pos = positions[t];
     const int* table = page_table + (int64_t)seq_of_token[t] * table_width;
-    float* qs = qs_all + warp * d;
-    for (int x = lane; x < d; x += 32) qs[x] = ld(q + ((int64_t)t * H + h) * d + x);
-    __syncwarp();
+    const int d_pad = (d + 3) & ~3, e_pad = 128 * E_CHUNKS;
+    float* qs = smem;                           // [d]
+    float* ms = qs + d_pad;                     // [warps] maxima, then [warps] sums
+    float* accs = ms + 2 * n_warps;             // [warps][e_pad]
+    for (int x = threadIdx.x; x < d; x += blockDim.x) qs[x] = ld(q + ((int64_t)t * H + h) * d + x);
+    __syncthreads();
     const int64_t page_elems = (int64_t)G * kPage * (d + e);
     const int64_t v_off = (int64_t)G * kPage * d;
-    float m = sink ? sink[h] : -INFINITY, l = sink ? 1.f : 0.f;
-    float acc[E_PER_LANE];
+    constexpr int VN = Vec16<T>::N;
+    const bool k_vec = d % VN == 0 && (((uintptr_t)kv) & 15) == 0 && (page_elems * sizeof(T)) % 16 == 0;
+    const bool v_vec = e % 4 == 0 && (((uintptr_t)kv) & 15) == 0 && (page_elems * sizeof(T)) % 16 == 0 && (v_off * sizeof(T)) % 16 == 0;
+    float m = -INFINITY, l = 0.f;
+    float acc[4 * E_CHUNKS];
 #pragma unroll
-    for (int c = 0; c < E_PER_LANE; ++c) acc[c] = 0.f;
-    for (int j0 = first_visible(pos, mask, mask_size); j0 <= pos; j0 += 32) {
+    for (int c = 0; c < 4 * E_CHUNKS; ++c) acc[c] = 0.f;
+    for (int j0 = first_visible(pos, mask, mask_size) + 32 * warp; j0 <= pos; j0 += 32 * n_warps) {
         const int j = j0 + lane;
         float s = -INFINITY;
         if (j <= pos) {
             const T* kp = kv + table[j / kPage] * page_elems + ((int64_t)g * kPage + (j % kPage)) * d;
             float dot = 0.f;
-            for (int x = 0; x < d; ++x) dot = fmaf(qs[x], ld(kp + x), dot);
+            if (k_vec) {
+                for (int x = 0; x < d; x += VN) {
+                    Vec16<T> kk;
+                    kk.load(kp + x);
+#pragma unroll
+                    for (int i = 0; i < VN; ++i) dot = fmaf(qs[x + i], kk.v[i], dot);
+                }
+            } else {
+                for (int x = 0; x < d; ++x) dot = fmaf(qs[x], ld(kp + x), dot);
+            }
             s = dot * scale;
         }
         const float m_new = fmaxf(m, warp_max(s));            // finite: key j0 is visible
-        const float corr = expf(m - m_new);                    // (m = -inf at first without a sink: 0)
+        const float corr = expf(m - m_new);                    // (m = -inf at first: 0)
         const float p = j <= pos ? expf(s - m_new) : 0.f;
         l = l * corr + warp_sum(p);
         m = m_new;
 #pragma unroll
-        for (int c = 0; c < E_PER_LANE; ++c) acc[c] *= corr;
+        for (int c = 0; c < 4 * E_CHUNKS; ++c) acc[c] *= corr;
         const int n_keys = min(32, pos - j0 + 1);
+#pragma unroll 4
         for (int jj = 0; jj < n_keys; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const int key = j0 + jj;
             const T* vp = kv + table[key / kPage] * page_elems + v_off + ((int64_t)g * kPage + (key % kPage)) * e;
 #pragma unroll
-            for (int c = 0; c < E_PER_LANE; ++c) {
-                const int x = lane + 32 * c;
-                if (x < e) acc[c] = fmaf(pj, ld(vp + x), acc[c]);
+            for (int c = 0; c < E_CHUNKS; ++c) {
+                const int x = 128 * c + 4 * lane;
+                if (v_vec) {
+                    if (x < e) {
+                        float vv[4];
+                        load4(vp + x, vv);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) acc[4 * c + i] = fmaf(pj, vv[i], acc[4 * c + i]);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (x + i < e) acc[4 * c + i] = fmaf(pj, ld(vp + x + i), acc[4 * c + i]);
+                }
             }
         }
     }
-    const float inv = 1.0f / l;
-#pragma unroll
-    for (int c = 0; c < E_PER_LANE; ++c) {
-        const int x = lane + 32 * c;
-        if (x < e) st(out + ((int64_t)t * H + h) * e + x, acc[c] * inv);
+    if (lane == 0) {
+        ms[warp] = m;
+        ms[n_warps + warp] = l;
     }
+#pragma unroll
+    for (int c = 0; c < E_CHUNKS; ++c)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) accs[warp * e_pad + 128 * c + 4 * lane + i] = acc[4 * c + i];
+    __syncthreads();
+    if (warp != 0) return;
+    float big = sink ? sink[h] : -INFINITY;
+    for (int w = 0; w < n_warps; ++w) big = fmaxf(big, ms[w]);              // finite: warp 0 holds the first visible key
+    float total = sink ? expf(sink[h] - big) : 0.f;
+#pragma unroll
+    for (int c = 0; c < 4 * E_CHUNKS; ++c) acc[c] = 0.f;
+    for (int w = 0; w < n_warps; ++w) {
+        const float f = ms[w] == -INFINITY ? 0.f : expf(ms[w] - big);
+        total += ms[n_warps + w] * f;
+#pragma unroll
+        for (int c = 0; c < E_CHUNKS; ++c)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[4 * c + i] = fmaf(accs[w * e_pad + 128 * c + 4 * lane + i], f, acc[4 * c + i]);
+    }
+    const float inv = 1.0f / total;
+#pragma unroll
+    for (int c = 0; c < E_CHUNKS; ++c)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int x = 128 * c + 4 * lane + i;
+            if (x < e) st(out + ((int64_t)t * H + h) * e + x, acc[4 * c + i] * inv);
+        }
 }
 
 template <typename T>
@@ -208,13 +294,13 @@ int attn_masked(const void* q, const void* kv, void* out, const int* seq_of_toke
                 const int* page_table, int table_width, int n, int H, int G, int d, int e, float scale, int mask,
                 int mask_size, const float* sink, cudaStream_t s) {
     WICK_REQUIRE(H > 0 && G > 0 && H % G == 0 && d > 0 && e > 0, "attn_masked: bad head counts or sizes");
-    WICK_REQUIRE(e <= 32 * E_PER_LANE, "attn_masked: a value size of %d is beyond %d", e, 32 * E_PER_LANE);
+    WICK_REQUIRE(e <= 128 * E_CHUNKS, "attn_masked: a value size of %d is beyond %d", e, 128 * E_CHUNKS);
     WICK_REQUIRE(mask == MASK_CAUSAL || mask_size > 0, "attn_masked: the mask needs a positive size");
     if (n == 0) return 0;
-    const int warps = 4;
-    const size_t smem = (size_t)warps * d * sizeof(float);
-    WICK_REQUIRE(smem <= 48 * 1024, "attn_masked: a head size of %d is beyond %d", d, 48 * 1024 / 4 / warps);
-    WICK_CUDA(launch(attn_masked_kernel<T>, dim3(ceil_div((int64_t)n * H, warps)), dim3(warps * 32), smem, s, (const T*)q,
+    const int warps = (int64_t)n * H <= 8192 ? 8 : 1;
+    const size_t smem = (size_t)(((d + 3) & ~3) + 2 * warps + warps * 128 * E_CHUNKS) * sizeof(float);
+    WICK_REQUIRE(smem <= 48 * 1024, "attn_masked: a head size of %d is beyond one block's shared memory", d);
+    WICK_CUDA(launch(attn_masked_kernel<T>, dim3((unsigned)((int64_t)n * H)), dim3(warps * 32), smem, s, (const T*)q,
                      (const T*)kv, (T*)out, seq_of_token, positions, page_table, table_width, n, H, G, d, e, scale, mask,
                      mask_size, sink));
     return check_launch("attn_masked");

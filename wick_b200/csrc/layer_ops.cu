@@ -11,34 +11,61 @@
 
 namespace wick {
 
-// One warp per row.  First pass: v = alpha x + sum of the partial sums (index order) goes
-// back to x and its squares are summed (lane l takes elements l, l + 32, ...; the 32 sums by
-// the butterfly); second pass: the same lane reads its own v again and writes y.  The order
-// of every sum depends on the width alone, so a row's bits do not depend on the batch.
+// x4 += the partial sums d_s[j .. j + 3], s in index order; the loads of four partial sums are issued together
+// (a chain of dependent trips to the L2 cache is what a step of few tokens would otherwise wait for).
+__device__ __forceinline__ void add_partials4(float4& v, const float* __restrict__ delta, int splits, int64_t split_stride, int64_t at) {
+    for (int s0 = 0; s0 < splits; s0 += 4) {
+        float4 d[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            d[u] = s0 + u < splits ? *reinterpret_cast<const float4*>(delta + (s0 + u) * split_stride + at) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            v.x += d[u].x; v.y += d[u].y; v.z += d[u].z; v.w += d[u].w;
+        }
+    }
+}
+
+// One block per row; the row waits in shared memory between the two passes.  First pass:
+// v = alpha x + the partial sums (index order) and the sum of its squares (a thread's elements in
+// index order, then the block's sum in thread order); second pass: y = v * scale * w to x and out.
+// The block's size depends on the width alone, so a row's bits do not depend on the batch.
 template <typename TOut>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(1024)
 scaled_add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int splits, int64_t split_stride,
                           float alpha, const float* __restrict__ w, float eps, TOut* __restrict__ out, int n, int width) {
+    extern __shared__ float smem[];
+    float* row = smem;
+    float* red = smem + ((width + 3) & ~3);
     pdl_trigger();
     pdl_wait();
     x = fresh(x);
     delta = fresh(delta);
-    const int lane = threadIdx.x & 31;
-    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (r >= n) return;
+    const int r = blockIdx.x;
     float* xr = x + (int64_t)r * width;
     float ss = 0.f;
-    for (int j = lane; j < width; j += 32) {
-        float v = alpha * xr[j];
-        for (int s = 0; s < splits; ++s) v += delta[s * split_stride + (int64_t)r * width + j];
-        xr[j] = v;
-        ss = fmaf(v, v, ss);
+    const bool vec = (width & 3) == 0 && (split_stride & 3) == 0;
+    if (vec) {
+        for (int j = threadIdx.x * 4; j < width; j += blockDim.x * 4) {
+            float4 v = *reinterpret_cast<const float4*>(xr + j);
+            v.x *= alpha; v.y *= alpha; v.z *= alpha; v.w *= alpha;
+            add_partials4(v, delta, splits, split_stride, (int64_t)r * width + j);
+            *reinterpret_cast<float4*>(row + j) = v;
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+    } else {
+        for (int j = threadIdx.x; j < width; j += blockDim.x) {
+            float v = alpha * xr[j];
+            for (int s = 0; s < splits; ++s) v += delta[s * split_stride + (int64_t)r * width + j];
+            row[j] = v;
+            ss = fmaf(v, v, ss);
+        }
     }
-    ss = warp_sum(ss);
+    ss = block_sum(ss, red);
     const float scale = 1.0f / sqrtf(ss / (float)width + eps);
     TOut* o = out ? out + (int64_t)r * width : nullptr;
-    for (int j = lane; j < width; j += 32) {
-        const float y = (xr[j] * scale) * w[j];
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        const float y = (row[j] * scale) * w[j];
         xr[j] = y;
         if (o) st(o + j, y);
     }
@@ -79,8 +106,16 @@ int scaled_add_rmsnorm(float* x, const float* delta, int splits, float alpha, co
                        int width, cudaStream_t s) {
     WICK_REQUIRE(width > 0 && n >= 0 && splits >= 0, "scaled_add_rmsnorm: bad sizes");
     if (n == 0) return 0;
-    WICK_CUDA(launch(scaled_add_rmsnorm_kernel<TOut>, dim3(ceil_div(n, 4)), dim3(128), 0, s, x, delta, splits,
-                     (int64_t)n * width, alpha, w, eps, (TOut*)out, n, width));
+    const size_t smem = ((size_t)((width + 3) & ~3) + 40) * sizeof(float);
+    WICK_REQUIRE(smem <= 200 * 1024, "scaled_add_rmsnorm: width %d is beyond one block's shared memory", width);
+    static bool raised = false;
+    if (smem > 48 * 1024 && !raised) {
+        WICK_CUDA(cudaFuncSetAttribute(scaled_add_rmsnorm_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        raised = true;
+    }
+    const int threads = min(1024, max(64, ((width + 3) / 4 + 31) / 32 * 32));
+    WICK_CUDA(launch(scaled_add_rmsnorm_kernel<TOut>, dim3(n), dim3(threads), smem, s, x, delta, splits, (int64_t)n * width, alpha,
+                     w, eps, (TOut*)out, n, width));
     return check_launch("scaled_add_rmsnorm");
 }
 

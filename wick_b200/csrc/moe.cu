@@ -5,9 +5,9 @@
 //   moe_down : out[t] = base[t] + weight * (down_{e(t,0)} hidden[t][0] + down_{e(t,1)} hidden[t][1] + ...)
 //              (choices in table order; base: float32 partial sums of a part that runs for every token)
 //
-// This form walks the tokens: every (token, choice) reads its expert's matrices (from the L2
-// cache when several tokens share an expert).  It is the form of decode steps and of the 32-bit
-// path.  Products accumulate in float32 along the inner dimension in a fixed order (lane l takes
+// These kernels are the form of decode steps and of the 32-bit path.  Up to 12,000 (token, choice)
+// pairs a step they run by expert (a matrix row is read once for all the pairs that use it); beyond
+// that every pair reads its expert's matrices itself (from the L2 cache when pairs share one).  Products accumulate in float32 along the inner dimension in a fixed order (lane l takes
 // elements l, l + 32, ... or the 8 neighbours at 8 l, 8 l + 256, ...; the 32 sums by the butterfly).
 #include "common.cuh"
 
@@ -87,6 +87,88 @@ moe_down_kernel(const T* __restrict__ hidden, const int* __restrict__ tokens, co
     }
 }
 
+// ---- by expert: every matrix row is read once for all the step's tokens that use it -----------
+// grid (experts, ceil(rows / (4 warps x ROWS_PER_WARP))).  A block lists the (token, choice) pairs of its
+// expert (in no order: every pair's result is computed on its own), leaves if there are none, and
+// then its warps take matrix rows: a row (for the gated pair: the gate row and the up row) is
+// multiplied with the inputs of four pairs at a time, 16 bytes a lane and trip, float32 sums (a
+// lane's elements in index order, the 32 lanes by the butterfly).
+//   GATED: in = x [n, k], w = [experts][2][rows][k], hidden[pair][row] = silu(g) * u
+//   else : in = hidden [n * top, k], w = [experts][rows][k], y[pair][row] = the product (float32)
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(128)
+moe_expert_rows_kernel(const T* __restrict__ in, const int* __restrict__ tokens, const int* __restrict__ table, int top,
+                       int n_pairs, const T* __restrict__ w, T* __restrict__ hidden_out, float* __restrict__ y_out, int rows,
+                       int k) {
+    extern __shared__ int list[];
+    __shared__ int count;
+    pdl_trigger();
+    pdl_wait();
+    in = fresh(in);
+    const int ex = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) count = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x)
+        if (table[(int64_t)tokens[p / top] * top + (p - p / top * top)] == ex) list[atomicAdd(&count, 1)] = p;
+    __syncthreads();
+    const int n_list = count;
+    if (n_list == 0) return;
+    constexpr int VN = Vec16<T>::N;
+    const bool vec = k % VN == 0 && ((((uintptr_t)w) | ((uintptr_t)in)) & 15) == 0;
+    const int r0 = (blockIdx.y * (blockDim.x >> 5) + warp) * ROWS_PER_WARP;
+    for (int r = r0; r < min(r0 + ROWS_PER_WARP, rows); ++r) {
+        const T* wg = w + (((int64_t)ex * (GATED ? 2 : 1)) * rows + r) * k;
+        const T* wu = wg + (int64_t)rows * k;
+        for (int m0 = 0; m0 < n_list; m0 += 4) {
+            const T* xin[4];
+            float ag[4] = {0.f, 0.f, 0.f, 0.f}, au[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int p = list[min(m0 + u, n_list - 1)];
+                xin[u] = in + (int64_t)(GATED ? p / top : p) * k;
+            }
+            if (vec) {
+                for (int j = lane * VN; j < k; j += 32 * VN) {
+                    Vec16<T> g, up;
+                    g.load(wg + j);
+                    if (GATED) up.load(wu + j);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        Vec16<T> xv;
+                        xv.load(xin[u] + j);
+#pragma unroll
+                        for (int i = 0; i < VN; ++i) {
+                            ag[u] = fmaf(g.v[i], xv.v[i], ag[u]);
+                            if (GATED) au[u] = fmaf(up.v[i], xv.v[i], au[u]);
+                        }
+                    }
+                }
+            } else {
+                for (int j = lane; j < k; j += 32) {
+                    const float g = ld(wg + j), up = GATED ? ld(wu + j) : 0.f;
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const float xv = ld(xin[u] + j);
+                        ag[u] = fmaf(g, xv, ag[u]);
+                        if (GATED) au[u] = fmaf(up, xv, au[u]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float g = warp_sum(ag[u]), up = GATED ? warp_sum(au[u]) : 0.f;
+                if (lane == 0 && m0 + u < n_list) {
+                    const int p = list[m0 + u];
+                    if (GATED) st(hidden_out + (int64_t)p * rows + r, g / (1.0f + expf(-g)) * up);
+                    else y_out[(int64_t)p * rows + r] = g;
+                }
+            }
+        }
+    }
+}
+
+constexpr int PAIRS_BY_EXPERT = 12000;          // pairs whose list fits one block's shared memory
+
 // ---- the form for many tokens: rows sorted by expert ---------------------------------------
 // The (token, choice) pairs of a step, numbered t * top + c, are sorted by expert (pairs of one
 // expert keep their order), so that every expert's rows lie together and go through an ordinary
@@ -158,7 +240,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
     for (int j = threadIdx.x; j < width; j += blockDim.x) {
         float sum = 0.f;
         for (int c = 0; c < top; ++c) {
-            const int row = row_of[t * top + c];
+            const int row = row_of ? row_of[t * top + c] : t * top + c;
             if (row >= 0) sum += y[(int64_t)row * width + j];
         }
         float v = 0.f;
@@ -173,6 +255,12 @@ int moe_up(const void* x, const int* tokens, const int* table, int top, int n_ex
     WICK_REQUIRE(top > 0 && n_experts > 0 && width > 0 && ff > 0, "moe_up: bad sizes");
     if (n == 0) return 0;
     const int warps = 4;
+    if ((int64_t)n * top <= PAIRS_BY_EXPERT) {
+        WICK_CUDA(launch(moe_expert_rows_kernel<T, true>, dim3(n_experts, ceil_div(ff, warps * ROWS_PER_WARP)), dim3(warps * 32),
+                         (size_t)n * top * sizeof(int), s, (const T*)x, tokens, table, top, n * top, (const T*)gate_up, (T*)hidden,
+                         (float*)nullptr, ff, width));
+        return check_launch("moe_up");
+    }
     WICK_REQUIRE((size_t)width * 4 <= 48 * 1024, "moe_up: width %d is beyond %d", width, 48 * 1024 / 4);
     WICK_CUDA(launch(moe_up_kernel<T>, dim3(n * top, ceil_div(ff, warps * ROWS_PER_WARP)), dim3(warps * 32), (size_t)width * 4, s,
                      (const T*)x, tokens, table, top, n_experts, (const T*)gate_up, (T*)hidden, width, ff));
@@ -181,10 +269,19 @@ int moe_up(const void* x, const int* tokens, const int* table, int top, int n_ex
 
 template <typename T>
 int moe_down(const void* hidden, const int* tokens, const int* table, int top, int n_experts, const void* down, float weight,
-             const float* base, int base_splits, float* out, int n, int width, int ff, cudaStream_t s) {
+             const float* base, int base_splits, float* y, float* out, int n, int width, int ff, cudaStream_t s) {
     WICK_REQUIRE(top > 0 && n_experts > 0 && width > 0 && ff > 0, "moe_down: bad sizes");
     if (n == 0) return 0;
     const int warps = 4;
+    if (y && (int64_t)n * top <= PAIRS_BY_EXPERT) {
+        // y [n * top, width] (float32, zero on entry): every pair's product, then the sum per token
+        WICK_CUDA(launch(moe_expert_rows_kernel<T, false>, dim3(n_experts, ceil_div(width, warps * ROWS_PER_WARP)), dim3(warps * 32),
+                         (size_t)n * top * sizeof(int), s, (const T*)hidden, tokens, table, top, n * top, (const T*)down, (T*)nullptr,
+                         y, width, ff));
+        WICK_CUDA(launch(moe_combine_kernel, dim3(n), dim3(256), 0, s, (const float*)y, (const int*)nullptr, top, weight, base,
+                         base_splits, (int64_t)n * width, out, width));
+        return check_launch("moe_down");
+    }
     const size_t smem = (size_t)top * ff * 4;
     WICK_REQUIRE(smem <= 48 * 1024, "moe_down: %d choices of %d numbers are beyond one block's shared memory", top, ff);
     WICK_CUDA(launch(moe_down_kernel<T>, dim3(n, ceil_div(width, warps * ROWS_PER_WARP)), dim3(warps * 32), smem, s,
@@ -207,14 +304,18 @@ WICK_API int wick_moe_up_f32(const void* x, const int* tokens, const int* table,
     return moe_up<float>(x, tokens, table, top, n_experts, gate_up, hidden, n, width, ff, (cudaStream_t)s);
 }
 WICK_API int wick_moe_down_bf16(const void* hidden, const int* tokens, const int* table, int top, int n_experts, const void* down,
-                                float weight, const float* base, int base_splits, float* out, int n, int width, int ff, void* s) {
-    return moe_down<bf16>(hidden, tokens, table, top, n_experts, down, weight, base, base_splits, out, n, width, ff, (cudaStream_t)s);
+                                float weight, const float* base, int base_splits, float* y, float* out, int n, int width, int ff,
+                                void* s) {
+    return moe_down<bf16>(hidden, tokens, table, top, n_experts, down, weight, base, base_splits, y, out, n, width, ff,
+                          (cudaStream_t)s);
 }
 WICK_API int wick_moe_down_f32(const void* hidden, const int* tokens, const int* table, int top, int n_experts, const void* down,
-                               float weight, const float* base, int base_splits, float* out, int n, int width, int ff, void* s) {
-    return moe_down<float>(hidden, tokens, table, top, n_experts, down, weight, base, base_splits, out, n, width, ff,
+                               float weight, const float* base, int base_splits, float* y, float* out, int n, int width, int ff,
+                               void* s) {
+    return moe_down<float>(hidden, tokens, table, top, n_experts, down, weight, base, base_splits, y, out, n, width, ff,
                            (cudaStream_t)s);
 }
+WICK_API int wick_moe_pairs_by_expert() { return PAIRS_BY_EXPERT; }
 
 // expert_of, row_of: int32 [n * top]; counts: int32 [experts], zero on entry.
 WICK_API int wick_moe_route(const int* tokens, const int* table, int top, int n_experts, int* expert_of, int* counts,

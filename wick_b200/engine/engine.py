@@ -349,8 +349,9 @@ class Engine:
         width = max(1, max((k + PAGE - 1) // PAGE for k in kv_lens))
         layout = BatchLayout(B, sum(q_lens), width, sum(len(w) for w in want))
         pages = [cache.pages_of(s)[:(k + PAGE - 1) // PAGE] for s, k in zip(slots, kv_lens)]
-        dev, _ = self._upload(layout, None, tokens=tokens, starts=starts, slots=slots, pages=pages, want=want)
-        batch = StepBatch(layout, dev, q_lens=q_lens, starts=starts, workspace=self.workspace)
+        dev, arr = self._upload(layout, None, tokens=tokens, starts=starts, slots=slots, pages=pages, want=want)
+        # (host: the description as the host wrote it, for parts that plan their launches by the step's token ids)
+        batch = StepBatch(layout, dev, q_lens=q_lens, starts=starts, workspace=self.workspace, host=arr)
         with ops.stream_scope():
             logits = self.model.forward(batch, cache)
         self._count_step()

@@ -707,8 +707,10 @@ def moe_table_down(hidden: torch.Tensor, tokens: torch.Tensor, table: torch.Tens
         _need(base.dim() == 3 and tuple(base.shape[1:]) == (n, width), f"base must be [splits, {n}, {width}]")
         splits = base.shape[0]
     out = torch.empty((n, width), dtype=torch.float32, device=hidden.device)
-    _layer().call(f"wick_moe_down_{_dt(hidden)}", "pppiipfpipiiip", _p(hidden), _p(tokens), _p(table), top, down.shape[0],
-                  _p(down), float(weight), _p(base), splits, _p(out), n, width, ff, _stream())
+    # (few pairs: the kernel leaves every pair's product in y and sums them per token afterwards)
+    y = torch.zeros((n * top, width), dtype=torch.float32, device=hidden.device) if n * top <= 12000 else None
+    _layer().call(f"wick_moe_down_{_dt(hidden)}", "pppiipfpippiiip", _p(hidden), _p(tokens), _p(table), top, down.shape[0],
+                  _p(down), float(weight), _p(base), splits, _p(y), _p(out), n, width, ff, _stream(), kernels=2 if y is not None else 1)
     return out
 
 

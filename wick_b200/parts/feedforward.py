@@ -24,6 +24,7 @@ from __future__ import annotations
 
 from typing import List, Optional
 
+import numpy as np
 import torch
 
 from .. import ops
@@ -123,7 +124,8 @@ class TableMoE(FeedForward):
                                                  hold(fetch(self._expert(i, "up")), "matrix")]) for i in range(self.experts)])
         self.down = torch.stack([hold(fetch(self._expert(i, "down")), "matrix") for i in range(self.experts)])
         self.table = hold(fetch(self.names["table"]), "table")
-        lo, hi = int(self.table.min()), int(self.table.max())
+        self.table_host = self.table.cpu().numpy()
+        lo, hi = int(self.table_host.min()), int(self.table_host.max())
         if lo < 0 or hi >= self.experts:
             raise ValueError(f"the expert table names expert {lo if lo < 0 else hi}; there are {self.experts}")
         if self.shared is not None:
@@ -177,14 +179,21 @@ class TableMoE(FeedForward):
         return ops.moe_table_down(hidden, batch.tokens, self.table, self.down, 1.0 / self.top, base).unsqueeze(0)
 
     # From this many tokens on a step (that is not being captured) sorts its rows by expert and
-    # runs every expert's rows through the tensor-core products; the host reads the experts' row
-    # counts for that (one wait per layer).  Fewer tokens walk their experts' matrices one by one.
+    # runs every expert's rows through the tensor-core products.  The host has to know the experts'
+    # row counts for that: it counts them itself from the step's token ids where the step's
+    # description has them (the table is a constant), and otherwise reads the device's counts
+    # (one wait per layer).  Fewer tokens go through the kernels that walk the matrices by expert.
     SORTED_FROM = 64
 
     def _forward_sorted(self, x, batch, base):
         n, dt = x.shape[0], self.ctx.dtype
         counts, row_of = ops.moe_route(batch.tokens, self.table, self.experts)
-        counts = counts.tolist()                            # (the host waits here)
+        host = getattr(batch, "host", None)
+        if host is not None:
+            ids = host[batch.layout.tokens:batch.layout.tokens + n]
+            counts = np.bincount(self.table_host[ids].ravel(), minlength=self.experts).tolist()
+        else:
+            counts = counts.tolist()                        # (the host waits here)
         rows = sum(counts)
         xs = ops.moe_gather(x, row_of, rows)
         hidden = torch.empty((rows, self.intermediate), dtype=dt, device=x.device)
