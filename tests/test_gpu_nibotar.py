@@ -152,9 +152,10 @@ def test_projection_finish(H, G, d, e, span, rot, pairing):
     lam = torch.tensor([0.3])
     batch = one_seq_batch(n, start, pages=[3, 1])
     kv = torch.full((5, G * PAGE * (d + e)), float("nan"), device=DEV)
+    cs = ops.rope_table(batch.positions, inv.to(DEV)) if rot else None
     q = ops.qkv_finish(parts.to(DEV), H, G, d, e, dtype=torch.float32, bias=bias.to(DEV),
                        q_weight=qw.to(DEV) if span else None, k_weight=kw.to(DEV) if span else None, eps=1e-5,
-                       inv_freq=inv.to(DEV) if rot else None, rot_dims=rot, pairing=pairing, v_keep=v_first.to(DEV), v_mode=2,
+                       cos=cs[0] if rot else None, sin=cs[1] if rot else None, rot_dims=rot, pairing=pairing, v_keep=v_first.to(DEV), v_mode=2,
                        blend=lam.to(DEV), kv=kv, page_table=batch.page_table, seq_of_token=batch.seq_of_token,
                        positions=batch.positions)
     row = parts.double().sum(0) + bias.double()

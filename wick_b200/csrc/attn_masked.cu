@@ -27,24 +27,29 @@ __device__ __forceinline__ int first_visible(int p, int mask, int size) {
 
 // ---------------------------------------------------------------------------
 // One block per token.  The row [q | k | v] (H d + G d + G e numbers) is summed into shared
-// memory; then, in this order: biases, the norms (a warp per span), the rotation, the value
+// memory; then, in this order: biases, the norms, the rotation (angles from the step's tables), the value
 // blend, and the stores.
 //   v_mode 0: values as projected; 1: also kept in v_keep [n, G e] (float32) for later layers;
 //   2: v <- (1 - lambda) v + lambda v_keep.
 //   pairing 0: (2i, 2i + 1) rotate together; 1: (i, i + rot_dims / 2).
+constexpr int MAX_SPANS = 512;                  // spans of the two norms together (a span per head at most)
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 qkv_finish_kernel(const float* __restrict__ parts, int splits, int64_t split_stride, const float* __restrict__ bias,
                   int H, int G, int d, int e, const float* __restrict__ q_w, int q_span, const float* __restrict__ k_w,
-                  int k_span, float eps, const float* __restrict__ inv_freq, int rot_dims, int pairing,
-                  float* __restrict__ v_keep, int v_mode, const float* __restrict__ lambda, T* __restrict__ q_out,
+                  int k_span, float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_dims,
+                  int pairing, float* __restrict__ v_keep, int v_mode, const float* __restrict__ lambda, T* __restrict__ q_out,
                   T* __restrict__ kv, const int* __restrict__ page_table, int table_width,
                   const int* __restrict__ seq_of_token, const int* __restrict__ positions, int write_kv) {
     extern __shared__ float row[];
+    __shared__ float partial[MAX_SPANS], span_scale[MAX_SPANS];
     pdl_trigger();
     pdl_wait();
     parts = fresh(parts);
     v_keep = fresh(v_keep);
+    cos_t = fresh(cos_t);
+    sin_t = fresh(sin_t);
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
     const int Wq = H * d, Wk = G * d, Wv = G * e, W = Wq + Wk + Wv;
     if ((W & 3) == 0 && (split_stride & 3) == 0) {
@@ -77,28 +82,41 @@ qkv_finish_kernel(const float* __restrict__ parts, int splits, int64_t split_str
         }
     }
     __syncthreads();
-    const int nq = q_w ? Wq / q_span : 0, nk = k_w ? Wk / k_span : 0;
-    for (int seg = warp; seg < nq + nk; seg += n_warps) {
-        const bool is_q = seg < nq;
-        const int span = is_q ? q_span : k_span;
-        float* p = row + (is_q ? seg * q_span : Wq + (seg - nq) * k_span);
-        const float* w = is_q ? q_w : k_w;
-        float ss = 0.f;
-        for (int j = lane; j < span; j += 32) ss = fmaf(p[j], p[j], ss);
-        ss = warp_sum(ss);
-        const float scale = 1.0f / sqrtf(ss / (float)span + eps);
-        for (int j = lane; j < span; j += 32) p[j] = (p[j] * scale) * w[j];
+    // The norms: every span's sum of squares is made by `per` warps (each a slice of the span: lane l its
+    // elements l, l + 32, ...; the 32 sums by the butterfly), the slices' sums are added in index order.
+    const int nq = q_w ? Wq / q_span : 0, nk = k_w ? Wk / k_span : 0, n_spans = nq + nk;
+    if (n_spans > 0) {
+        const int per = max(1, n_warps / n_spans);
+        for (int unit = warp; unit < n_spans * per; unit += n_warps) {
+            const int seg = unit / per, part = unit - seg * per;
+            const bool is_q = seg < nq;
+            const int span = is_q ? q_span : k_span;
+            const float* p = row + (is_q ? seg * q_span : Wq + (seg - nq) * k_span);
+            const int lo = (int)((int64_t)span * part / per), hi = (int)((int64_t)span * (part + 1) / per);
+            float ss = 0.f;
+            for (int j = lo + lane; j < hi; j += 32) ss = fmaf(p[j], p[j], ss);
+            ss = warp_sum(ss);
+            if (lane == 0) partial[unit] = ss;
+        }
+        __syncthreads();
+        for (int seg = tid; seg < n_spans; seg += blockDim.x) {
+            float ss = 0.f;
+            for (int part = 0; part < per; ++part) ss += partial[seg * per + part];
+            span_scale[seg] = 1.0f / sqrtf(ss / (float)(seg < nq ? q_span : k_span) + eps);
+        }
+        __syncthreads();
+        for (int j = tid; j < (q_w ? Wq : 0); j += blockDim.x) row[j] = (row[j] * span_scale[j / q_span]) * q_w[j % q_span];
+        for (int j = tid; j < (k_w ? Wk : 0); j += blockDim.x) row[Wq + j] = (row[Wq + j] * span_scale[nq + j / k_span]) * k_w[j % k_span];
+        __syncthreads();
     }
-    __syncthreads();
     const int pos = positions[t];
-    if (inv_freq && rot_dims > 0) {
+    if (cos_t && rot_dims > 0) {
         const int half = rot_dims >> 1;
         for (int idx = tid; idx < (H + G) * half; idx += blockDim.x) {
             const int h = idx / half, i = idx - h * half;
             float* p = row + h * d;                       // (the k heads follow the q heads at the same stride)
             const int j0 = pairing == 0 ? 2 * i : i, j1 = pairing == 0 ? 2 * i + 1 : i + half;
-            float sn, cs;
-            sincosf((float)pos * inv_freq[i], &sn, &cs);
+            const float cs = cos_t[(int64_t)t * half + i], sn = sin_t[(int64_t)t * half + i];
             const float u = p[j0], v = p[j1];
             p[j0] = u * cs - v * sn;
             p[j1] = v * cs + u * sn;
@@ -182,9 +200,13 @@ attn_masked_kernel(const T* __restrict__ q, const T* __restrict__ kv, T* __restr
     for (int c = 0; c < 4 * E_CHUNKS; ++c) acc[c] = 0.f;
     for (int j0 = first_visible(pos, mask, mask_size) + 32 * warp; j0 <= pos; j0 += 32 * n_warps) {
         const int j = j0 + lane;
+        // a tile of 32 keys lies in one page or in two: both are looked up once, ahead of the rows
+        const int first_page = j0 / kPage;
+        const int64_t page_a = table[first_page] * page_elems;
+        const int64_t page_b = (first_page + 1) * kPage <= min(pos, j0 + 31) ? table[first_page + 1] * page_elems : page_a;
         float s = -INFINITY;
         if (j <= pos) {
-            const T* kp = kv + table[j / kPage] * page_elems + ((int64_t)g * kPage + (j % kPage)) * d;
+            const T* kp = kv + (j / kPage == first_page ? page_a : page_b) + ((int64_t)g * kPage + (j % kPage)) * d;
             float dot = 0.f;
             if (k_vec) {
                 for (int x = 0; x < d; x += VN) {
@@ -210,7 +232,7 @@ attn_masked_kernel(const T* __restrict__ q, const T* __restrict__ kv, T* __restr
         for (int jj = 0; jj < n_keys; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const int key = j0 + jj;
-            const T* vp = kv + table[key / kPage] * page_elems + v_off + ((int64_t)g * kPage + (key % kPage)) * e;
+            const T* vp = kv + (key / kPage == first_page ? page_a : page_b) + v_off + ((int64_t)g * kPage + (key % kPage)) * e;
 #pragma unroll
             for (int c = 0; c < E_CHUNKS; ++c) {
                 const int x = 128 * c + 4 * lane;
@@ -264,15 +286,17 @@ attn_masked_kernel(const T* __restrict__ q, const T* __restrict__ kv, T* __restr
 
 template <typename T>
 int qkv_finish(const float* parts, int splits, int n, const float* bias, int H, int G, int d, int e, const float* q_w,
-               int q_span, const float* k_w, int k_span, float eps, const float* inv_freq, int rot_dims, int pairing,
-               float* v_keep, int v_mode, const float* lambda, void* q_out, void* kv, const int* page_table, int table_width,
-               const int* seq_of_token, const int* positions, int write_kv, cudaStream_t s) {
+               int q_span, const float* k_w, int k_span, float eps, const float* cos_t, const float* sin_t, int rot_dims,
+               int pairing, float* v_keep, int v_mode, const float* lambda, void* q_out, void* kv, const int* page_table,
+               int table_width, const int* seq_of_token, const int* positions, int write_kv, cudaStream_t s) {
     WICK_REQUIRE(H > 0 && G > 0 && H % G == 0 && d > 0 && e > 0, "qkv_finish: bad head counts or sizes");
     WICK_REQUIRE(splits >= 1, "qkv_finish: partial sums are needed");
     const int Wq = H * d, Wk = G * d;
     if (q_w) WICK_REQUIRE(q_span > 0 && Wq % q_span == 0, "qkv_finish: a q norm span of %d does not divide %d", q_span, Wq);
     if (k_w) WICK_REQUIRE(k_span > 0 && Wk % k_span == 0, "qkv_finish: a k norm span of %d does not divide %d", k_span, Wk);
     WICK_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= d, "qkv_finish: %d rotated dims of %d", rot_dims, d);
+    WICK_REQUIRE((cos_t == nullptr) == (sin_t == nullptr), "qkv_finish: the two angle tables come together");
+    WICK_REQUIRE((q_w ? Wq / q_span : 0) + (k_w ? Wk / k_span : 0) <= MAX_SPANS, "qkv_finish: too many norm spans");
     WICK_REQUIRE(v_mode == 0 || v_keep, "qkv_finish: the kept values are missing");
     WICK_REQUIRE(v_mode != 2 || lambda, "qkv_finish: the blend factor is missing");
     if (n == 0) return 0;
@@ -284,7 +308,7 @@ int qkv_finish(const float* parts, int splits, int n, const float* bias, int H, 
         raised = true;
     }
     WICK_CUDA(launch(qkv_finish_kernel<T>, dim3(n), dim3(256), smem, s, parts, splits, (int64_t)n * (Wq + Wk + G * e), bias, H, G,
-                     d, e, q_w, q_span, k_w, k_span, eps, inv_freq, rot_dims, pairing, v_keep, v_mode, lambda, (T*)q_out,
+                     d, e, q_w, q_span, k_w, k_span, eps, cos_t, sin_t, rot_dims, pairing, v_keep, v_mode, lambda, (T*)q_out,
                      (T*)kv, page_table, table_width, seq_of_token, positions, write_kv));
     return check_launch("qkv_finish");
 }
@@ -313,10 +337,11 @@ typedef __nv_bfloat16 bf16;
 
 #define WICK_QKV_FINISH(NAME, T)                                                                                              \
     WICK_API int NAME(const float* parts, int splits, int n, const float* bias, int H, int G, int d, int e, const float* q_w,    \
-                      int q_span, const float* k_w, int k_span, float eps, const float* inv_freq, int rot_dims, int pairing,     \
-                      float* v_keep, int v_mode, const float* lambda, void* q_out, void* kv, const int* page_table,              \
-                      int table_width, const int* seq_of_token, const int* positions, int write_kv, void* s) {                   \
-        return qkv_finish<T>(parts, splits, n, bias, H, G, d, e, q_w, q_span, k_w, k_span, eps, inv_freq, rot_dims, pairing,      \
+                      int q_span, const float* k_w, int k_span, float eps, const float* cos_t, const float* sin_t,               \
+                      int rot_dims, int pairing, float* v_keep, int v_mode, const float* lambda, void* q_out, void* kv,          \
+                      const int* page_table, int table_width, const int* seq_of_token, const int* positions, int write_kv,       \
+                      void* s) {                                                                                                 \
+        return qkv_finish<T>(parts, splits, n, bias, H, G, d, e, q_w, q_span, k_w, k_span, eps, cos_t, sin_t, rot_dims, pairing,  \
                              v_keep, v_mode, lambda, q_out, kv, page_table, table_width, seq_of_token, positions, write_kv,      \
                              (cudaStream_t)s);                                                                                   \
     }

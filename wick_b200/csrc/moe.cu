@@ -90,9 +90,9 @@ moe_down_kernel(const T* __restrict__ hidden, const int* __restrict__ tokens, co
 // ---- by expert: every matrix row is read once for all the step's tokens that use it -----------
 // grid (experts, ceil(rows / (4 warps x ROWS_PER_WARP))).  A block lists the (token, choice) pairs of its
 // expert (in no order: every pair's result is computed on its own), leaves if there are none, and
-// then its warps take matrix rows: a row (for the gated pair: the gate row and the up row) is
-// multiplied with the inputs of four pairs at a time, 16 bytes a lane and trip, float32 sums (a
-// lane's elements in index order, the 32 lanes by the butterfly).
+// then its warps take matrix rows, four each (for the gated pair: four gate rows and four up rows),
+// and multiply them with the inputs of two pairs at a time, 16 bytes a lane and trip, float32 sums
+// (a lane's elements in index order, the 32 lanes by the butterfly).
 //   GATED: in = x [n, k], w = [experts][2][rows][k], hidden[pair][row] = silu(g) * u
 //   else : in = hidden [n * top, k], w = [experts][rows][k], y[pair][row] = the product (float32)
 template <typename T, bool GATED>
@@ -116,6 +116,54 @@ moe_expert_rows_kernel(const T* __restrict__ in, const int* __restrict__ tokens,
     constexpr int VN = Vec16<T>::N;
     const bool vec = k % VN == 0 && ((((uintptr_t)w) | ((uintptr_t)in)) & 15) == 0;
     const int r0 = (blockIdx.y * (blockDim.x >> 5) + warp) * ROWS_PER_WARP;
+    if (r0 >= rows) return;
+    if (vec && r0 + ROWS_PER_WARP <= rows) {
+        // the warp's rows side by side: their loads are in flight together, and an input's 16 bytes serve all of them
+        const T* wg = w + (((int64_t)ex * (GATED ? 2 : 1)) * rows + r0) * k;
+        const T* wu = wg + (int64_t)rows * k;
+        for (int m0 = 0; m0 < n_list; m0 += 2) {
+            const T* xin[2];
+            float ag[ROWS_PER_WARP][2], au[ROWS_PER_WARP][2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int p = list[min(m0 + u, n_list - 1)];
+                xin[u] = in + (int64_t)(GATED ? p / top : p) * k;
+#pragma unroll
+                for (int r = 0; r < ROWS_PER_WARP; ++r) ag[r][u] = au[r][u] = 0.f;
+            }
+            for (int j = lane * VN; j < k; j += 32 * VN) {
+                Vec16<T> g[ROWS_PER_WARP], up[ROWS_PER_WARP], xv[2];
+#pragma unroll
+                for (int r = 0; r < ROWS_PER_WARP; ++r) {
+                    g[r].load(wg + (int64_t)r * k + j);
+                    if (GATED) up[r].load(wu + (int64_t)r * k + j);
+                }
+#pragma unroll
+                for (int u = 0; u < 2; ++u) xv[u].load(xin[u] + j);
+#pragma unroll
+                for (int r = 0; r < ROWS_PER_WARP; ++r)
+#pragma unroll
+                    for (int u = 0; u < 2; ++u)
+#pragma unroll
+                        for (int i = 0; i < VN; ++i) {
+                            ag[r][u] = fmaf(g[r].v[i], xv[u].v[i], ag[r][u]);
+                            if (GATED) au[r][u] = fmaf(up[r].v[i], xv[u].v[i], au[r][u]);
+                        }
+            }
+#pragma unroll
+            for (int r = 0; r < ROWS_PER_WARP; ++r)
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const float gs = warp_sum(ag[r][u]), us = GATED ? warp_sum(au[r][u]) : 0.f;
+                    if (lane == 0 && m0 + u < n_list) {
+                        const int p = list[m0 + u];
+                        if (GATED) st(hidden_out + (int64_t)p * rows + r0 + r, gs / (1.0f + expf(-gs)) * us);
+                        else y_out[(int64_t)p * rows + r0 + r] = gs;
+                    }
+                }
+        }
+        return;
+    }
     for (int r = r0; r < min(r0 + ROWS_PER_WARP, rows); ++r) {
         const T* wg = w + (((int64_t)ex * (GATED ? 2 : 1)) * rows + r) * k;
         const T* wu = wg + (int64_t)rows * k;
@@ -127,31 +175,13 @@ moe_expert_rows_kernel(const T* __restrict__ in, const int* __restrict__ tokens,
                 const int p = list[min(m0 + u, n_list - 1)];
                 xin[u] = in + (int64_t)(GATED ? p / top : p) * k;
             }
-            if (vec) {
-                for (int j = lane * VN; j < k; j += 32 * VN) {
-                    Vec16<T> g, up;
-                    g.load(wg + j);
-                    if (GATED) up.load(wu + j);
+            for (int j = lane; j < k; j += 32) {
+                const float g = ld(wg + j), up = GATED ? ld(wu + j) : 0.f;
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        Vec16<T> xv;
-                        xv.load(xin[u] + j);
-#pragma unroll
-                        for (int i = 0; i < VN; ++i) {
-                            ag[u] = fmaf(g.v[i], xv.v[i], ag[u]);
-                            if (GATED) au[u] = fmaf(up.v[i], xv.v[i], au[u]);
-                        }
-                    }
-                }
-            } else {
-                for (int j = lane; j < k; j += 32) {
-                    const float g = ld(wg + j), up = GATED ? ld(wu + j) : 0.f;
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const float xv = ld(xin[u] + j);
-                        ag[u] = fmaf(g, xv, ag[u]);
-                        if (GATED) au[u] = fmaf(up, xv, au[u]);
-                    }
+                for (int u = 0; u < 4; ++u) {
+                    const float xv = ld(xin[u] + j);
+                    ag[u] = fmaf(g, xv, ag[u]);
+                    if (GATED) au[u] = fmaf(up, xv, au[u]);
                 }
             }
 #pragma unroll
@@ -172,7 +202,7 @@ constexpr int PAIRS_BY_EXPERT = 12000;          // pairs whose list fits one blo
 // ---- the form for many tokens: rows sorted by expert ---------------------------------------
 // The (token, choice) pairs of a step, numbered t * top + c, are sorted by expert (pairs of one
 // expert keep their order), so that every expert's rows lie together and go through an ordinary
-// matrix product.  route: expert_of[pair] and counts[expert]; place: row_of[pair] (a warp per
+// matrix product.  route: expert_of[pair] and counts[expert]; place: row_of[pair] (a block per
 // expert walks all pairs in order and numbers its own); gather: the sorted rows of x; combine:
 // out[t] = base[t] + weight * (y[row_of[t, 0]] + y[row_of[t, 1]] + ...), choices in table order.
 __global__ void moe_route_kernel(const int* __restrict__ tokens, const int* __restrict__ table, int top, int n_experts,
@@ -188,25 +218,36 @@ __global__ void moe_route_kernel(const int* __restrict__ tokens, const int* __re
     if (ex >= 0) atomicAdd(counts + ex, 1);               // (a count: the order of the additions does not matter)
 }
 
-__global__ void __launch_bounds__(32)
+__global__ void __launch_bounds__(1024)
 moe_place_kernel(const int* __restrict__ expert_of, const int* __restrict__ counts, int* __restrict__ row_of, int n_pairs) {
+    __shared__ int warp_count[32];
     pdl_trigger();
     pdl_wait();
     expert_of = fresh(expert_of);
     counts = fresh(counts);
-    const int ex = blockIdx.x, lane = threadIdx.x;
+    const int ex = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     int base = 0;
     for (int e = 0; e < ex; ++e) base += counts[e];
-    for (int i0 = 0; i0 < n_pairs; i0 += 32) {
-        const int i = i0 + lane;
-        const bool mine = i < n_pairs && expert_of[i] == ex;
+    // pairs in chunks of one per thread: a pair's row is the expert's first row plus the number of
+    // the expert's pairs before it (earlier chunks, earlier warps of the chunk, earlier lanes of the warp)
+    for (int i0 = 0; i0 < n_pairs; i0 += blockDim.x) {
+        const int i = i0 + threadIdx.x;
+        const int mine_ex = i < n_pairs ? expert_of[i] : -2;
+        const bool mine = mine_ex == ex;
         const unsigned m = __ballot_sync(0xffffffffu, mine);
-        if (mine) row_of[i] = base + __popc(m & ((1u << lane) - 1));
-        base += __popc(m);
+        if (lane == 0) warp_count[warp] = __popc(m);
+        __syncthreads();
+        int before = 0, total = 0;
+        for (int w = 0; w < n_warps; ++w) {
+            const int c = warp_count[w];
+            before += w < warp ? c : 0;
+            total += c;
+        }
+        if (mine) row_of[i] = base + before + __popc(m & ((1u << lane) - 1));
+        if (ex == 0 && mine_ex == -1) row_of[i] = -1;      // pairs without an expert have no row
+        base += total;
+        __syncthreads();
     }
-    if (ex == 0)                                           // pairs without an expert have no row
-        for (int i = lane; i < n_pairs; i += 32)
-            if (expert_of[i] < 0) row_of[i] = -1;
 }
 
 template <typename T>
@@ -325,8 +366,8 @@ WICK_API int wick_moe_route(const int* tokens, const int* table, int top, int n_
     const int pairs = n * top;
     WICK_CUDA(launch(moe_route_kernel, dim3(ceil_div(pairs, 256)), dim3(256), 0, (cudaStream_t)s, tokens, table, top, n_experts,
                      expert_of, counts, pairs));
-    WICK_CUDA(launch(moe_place_kernel, dim3(n_experts), dim3(32), 0, (cudaStream_t)s, (const int*)expert_of, (const int*)counts,
-                     row_of, pairs));
+    WICK_CUDA(launch(moe_place_kernel, dim3(n_experts), dim3(pairs >= 1024 ? 1024 : 256), 0, (cudaStream_t)s, (const int*)expert_of,
+                     (const int*)counts, row_of, pairs));
     return check_launch("moe_route");
 }
 WICK_API int wick_moe_gather_bf16(const void* x, const int* row_of, int top, void* xs, int n, int width, void* s) {

@@ -589,14 +589,15 @@ def _kv_pages(name: str, kv: torch.Tensor, dtype, n_kv: int, d: int, e: int) -> 
 
 def qkv_finish(parts: torch.Tensor, n_heads: int, n_kv: int, d: int, e: int, *, dtype: torch.dtype,
                bias: Optional[torch.Tensor] = None, q_weight: Optional[torch.Tensor] = None,
-               k_weight: Optional[torch.Tensor] = None, eps: float = 0.0, inv_freq: Optional[torch.Tensor] = None,
-               rot_dims: int = 0, pairing: str = "neighbours", v_keep: Optional[torch.Tensor] = None, v_mode: int = 0,
+               k_weight: Optional[torch.Tensor] = None, eps: float = 0.0, cos: Optional[torch.Tensor] = None,
+               sin: Optional[torch.Tensor] = None, rot_dims: int = 0, pairing: str = "neighbours", v_keep: Optional[torch.Tensor] = None, v_mode: int = 0,
                blend: Optional[torch.Tensor] = None, kv: Optional[torch.Tensor], page_table: torch.Tensor,
                seq_of_token: torch.Tensor, positions: torch.Tensor, write_kv: bool = True) -> torch.Tensor:
     """From the q/k/v projection's float32 partial sums ``parts`` [splits, n, H d + G d + G e]:
     biases, RMS norms of q and k over spans the length of their weight vectors (a head, or the
-    whole projection), rotation of the first ``rot_dims`` elements of every q and k head by
-    ``position * inv_freq[i]`` (``pairing``: which two elements turn together), the value blend
+    whole projection), rotation of the first ``rot_dims`` elements of every q and k head by the
+    angles whose ``cos`` and ``sin`` [n, rot_dims / 2] are given (``pairing``: which two elements
+    turn together), the value blend
     (``v_mode`` 1: the values are also kept in ``v_keep`` [n, G e]; 2: v <- (1 - blend) v + blend
     v_keep), then q -> the result [n, H, d] in ``dtype`` and k, v -> the token's place in ``kv``."""
     _cuda("parts", parts, torch.float32)
@@ -612,8 +613,9 @@ def qkv_finish(parts: torch.Tensor, n_heads: int, n_kv: int, d: int, e: int, *, 
     if k_weight is not None:
         _cuda("k_weight", k_weight, torch.float32)
         k_span = k_weight.numel()
-    if inv_freq is not None:
-        _cuda("inv_freq", inv_freq, torch.float32, (rot_dims // 2,))
+    if cos is not None:
+        _cuda("cos", cos, torch.float32, (n, rot_dims // 2))
+        _cuda("sin", sin, torch.float32, (n, rot_dims // 2))
     if v_mode:
         _cuda("v_keep", v_keep, torch.float32, (n, n_kv * e))
     if v_mode == 2:
@@ -625,9 +627,9 @@ def qkv_finish(parts: torch.Tensor, n_heads: int, n_kv: int, d: int, e: int, *, 
     _cuda("seq_of_token", seq_of_token, torch.int32, (n,))
     _cuda("positions", positions, torch.int32, (n,))
     q_out = torch.empty((n, n_heads, d), dtype=dtype, device=parts.device)
-    _layer().call(f"wick_qkv_finish_{_dt(q_out)}", "piipiiiipipifpiipippppippip", _p(parts), parts.shape[0], n, _p(bias),
-                  n_heads, n_kv, d, e, _p(q_weight), q_span, _p(k_weight), k_span, float(eps), _p(inv_freq),
-                  rot_dims if inv_freq is not None else 0, PAIRINGS[pairing], _p(v_keep), v_mode, _p(blend), _p(q_out),
+    _layer().call(f"wick_qkv_finish_{_dt(q_out)}", "piipiiiipipifppiipippppippip", _p(parts), parts.shape[0], n, _p(bias),
+                  n_heads, n_kv, d, e, _p(q_weight), q_span, _p(k_weight), k_span, float(eps), _p(cos), _p(sin),
+                  rot_dims if cos is not None else 0, PAIRINGS[pairing], _p(v_keep), v_mode, _p(blend), _p(q_out),
                   _p(kv) if write_kv else None, _p(page_table), page_table.shape[-1], _p(seq_of_token), _p(positions),
                   1 if write_kv else 0, _stream())
     return q_out

@@ -76,6 +76,14 @@ class RotaryPairs(Position):
     def rotary_inv_freq(self):
         return None                      # (not the whole-head half-split form that the fused q/k kernel knows)
 
+    def tables(self, batch):
+        """cos/sin [tokens, dims/2] of this step, computed once and shared by every layer that turns alike."""
+        key = ("rotary_pairs", self.dims, self.theta)
+        t = batch.memo.get(key)
+        if t is None:
+            t = batch.memo[key] = ops.rope_table(batch.positions, self.inv_freq)
+        return t
+
     def apply(self, q, k, positions):
         cos, sin = ops.rope_table(positions, self.inv_freq)
         half = self.dims // 2
@@ -214,10 +222,11 @@ class Attention(Mixer):
                     raise RuntimeError(f"no layer before this one left its values under {key[1]!r}")
                 v_mode = 2
         rot = self.position if isinstance(self.position, RotaryPairs) else None
+        cos, sin = rot.tables(batch) if rot else (None, None)
         q = ops.qkv_finish(
             parts, self.heads, self.kv_heads, self.head_dim, self.v_dim, dtype=self.ctx.dtype, bias=self.qkv_bias,
             q_weight=self.q_weight, k_weight=self.k_weight, eps=self.eps,
-            inv_freq=rot.inv_freq if rot else None, rot_dims=rot.dims if rot else 0,
+            cos=cos, sin=sin, rot_dims=rot.dims if rot else 0,
             pairing=rot.pairing if rot else "neighbours", v_keep=v_keep, v_mode=v_mode, blend=self.blend_factor,
             kv=cache.kv, page_table=batch.page_table, seq_of_token=batch.seq_of_token, positions=batch.positions,
             write_kv=write_cache)

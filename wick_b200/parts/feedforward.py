@@ -32,6 +32,17 @@ from .base import FeedForward, TensorSpec, build_part, register_part
 from .linear import Linear
 
 
+_streams = {}
+
+
+def _side_streams(device, n: int = 4):
+    """A few streams per device for work that a step forks and joins."""
+    key = torch.device(device)
+    if key not in _streams:
+        _streams[key] = [torch.cuda.Stream(device=key) for _ in range(n)]
+    return _streams[key]
+
+
 class NoFeedForward(FeedForward):
     PROMPT_CAPTURABLE = True
     IS_NONE = True
@@ -184,6 +195,7 @@ class TableMoE(FeedForward):
     # description has them (the table is a constant), and otherwise reads the device's counts
     # (one wait per layer).  Fewer tokens go through the kernels that walk the matrices by expert.
     SORTED_FROM = 64
+    ONE_STREAM_FROM = 1 << 16      # rows (over all experts) from which every expert fills the part alone
 
     def _forward_sorted(self, x, batch, base):
         n, dt = x.shape[0], self.ctx.dtype
@@ -198,12 +210,26 @@ class TableMoE(FeedForward):
         xs = ops.moe_gather(x, row_of, rows)
         hidden = torch.empty((rows, self.intermediate), dtype=dt, device=x.device)
         y = torch.empty((rows, self.width), dtype=torch.float32, device=x.device)
-        at = 0
+        # An expert's few hundred rows make fewer tiles than the part has multiprocessors, so the experts'
+        # products go to several streams and run side by side; the step's stream waits for all of them.
+        main = torch.cuda.current_stream()
+        side = _side_streams(x.device)
+        fork = torch.cuda.Event()
+        fork.record(main)
+        at, used = 0, []
         for i, c in enumerate(counts):
             if c:
-                self.expert_up[i]._tensor_core()._run(xs[at:at + c], hidden[at:at + c], 1)
-                self.expert_down[i]._tensor_core()._run(hidden[at:at + c], y[at:at + c], 1)
+                st = side[len(used) % len(side)] if rows < self.ONE_STREAM_FROM else main
+                if st is not main and st not in used:
+                    st.wait_event(fork)
+                with torch.cuda.stream(st), ops.stream_scope():
+                    self.expert_up[i]._tensor_core()._run(xs[at:at + c], hidden[at:at + c], 1)
+                    self.expert_down[i]._tensor_core()._run(hidden[at:at + c], y[at:at + c], 1)
+                if st is not main:
+                    used.append(st)
                 at += c
+        for st in set(used):
+            main.wait_stream(st)
         return ops.moe_combine(y, row_of, 1.0 / self.top, base).unsqueeze(0)
 
 
