@@ -228,8 +228,7 @@ attn_masked_kernel(const T* __restrict__ q, const T* __restrict__ kv, T* __restr
 #pragma unroll
         for (int c = 0; c < 4 * E_CHUNKS; ++c) acc[c] *= corr;
         const int n_keys = min(32, pos - j0 + 1);
-#pragma unroll 4
-        for (int jj = 0; jj < n_keys; ++jj) {
+        auto add_value = [&](int jj) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const int key = j0 + jj;
             const T* vp = kv + (key / kPage == first_page ? page_a : page_b) + v_off + ((int64_t)g * kPage + (key % kPage)) * e;
@@ -249,6 +248,12 @@ attn_masked_kernel(const T* __restrict__ q, const T* __restrict__ kv, T* __restr
                         if (x + i < e) acc[4 * c + i] = fmaf(pj, ld(vp + x + i), acc[4 * c + i]);
                 }
             }
+        };
+        if (n_keys == 32) {                                      // a whole tile: the 32 rows' loads are in flight together
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) add_value(jj);
+        } else {
+            for (int jj = 0; jj < n_keys; ++jj) add_value(jj);
         }
     }
     if (lane == 0) {

@@ -55,6 +55,10 @@ struct Params {
     long long ldo;
     void* out;
     int* status;
+    // Grouped form: B holds several matrices of `group_rows` rows each, one after the other, and every tile of
+    // 256 rows of A belongs to one of them: group_of_mtile[m0 / 256] (written by a kernel before this one).
+    const int* group_of_mtile;     // null: one matrix
+    int group_rows;
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -160,7 +164,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 tile_coords(w, m0, n0);
                 k_range(w, k0, k1);
                 const int a_row = m0 + rank * BM;
-                const int b_row = GATED ? (rank == 0 ? n0 : p.pair_offset + n0) : n0 + rank * BNH;
+                int b_row = GATED ? (rank == 0 ? n0 : p.pair_offset + n0) : n0 + rank * BNH;
+                if (p.group_of_mtile) {
+                    if (first) { pdl_wait(); first = false; }                                  // (the table comes from a kernel)
+                    b_row += __ldcg(p.group_of_mtile + m0 / (2 * BM)) * p.group_rows;
+                }
                 for (int i = k0; i < k1; ++i, ++it) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
@@ -332,10 +340,14 @@ using namespace wick;
 // (every element by one thread: no atomics).  b_packed: b in the tiled form described at wick_gemm_tc.
 // splits > 1 (plain float32 output without accumulation): run r of the inner dimension writes its
 // partial sums to out + r * split_stride.  status as in wick_gemm_tc.
-WICK_API int wick_gemm_tc2(const void* a, int a_rows, const void* b, long long b_total_rows, int b_rows, int k, int gated,
-                           int pair_offset, int out_f32, int accumulate, int b_packed, void* out, long long ldo, int splits,
-                           long long split_stride, int* status, void* stream) {
+// group_of_mtile: null, or int32 [ceil(a_rows / 256)] on the device: b then holds matrices of group_rows rows each
+// (b_rows outputs of each are computed), and rows 256 i .. of a are multiplied with matrix group_of_mtile[i].
+WICK_API int wick_gemm_tc2_grouped(const void* a, int a_rows, const void* b, long long b_total_rows, int b_rows, int k, int gated,
+                                   int pair_offset, int out_f32, int accumulate, int b_packed, void* out, long long ldo, int splits,
+                                   long long split_stride, const int* group_of_mtile, int group_rows, int* status, void* stream) {
     using namespace pair;
+    WICK_REQUIRE(!group_of_mtile || (group_rows > 0 && b_total_rows % group_rows == 0 && (!b_packed || group_rows % 128 == 0)),
+                 "gemm_tc2: matrices of %d rows in an operand of %lld", group_rows, b_total_rows);
     WICK_REQUIRE(a_rows > 0 && b_rows > 0 && k > 0, "gemm_tc2: bad sizes");
     WICK_REQUIRE(gated == 0 || gated == 1, "gemm_tc2: bad options");
     WICK_REQUIRE(!accumulate || (out_f32 && !gated), "gemm_tc2: accumulation goes with a plain float32 output");
@@ -349,6 +361,7 @@ WICK_API int wick_gemm_tc2(const void* a, int a_rows, const void* b, long long b
     Params p;
     p.a_rows = a_rows; p.b_rows = b_rows; p.k_blocks = ceil_div(k, BK); p.gated = gated; p.pair_offset = pair_offset;
     p.out_f32 = out_f32; p.ldo = ldo; p.out = out; p.status = status; p.b_packed = b_packed;
+    p.group_of_mtile = group_of_mtile; p.group_rows = group_rows;
     p.grid_m = ceil_div(a_rows, 2 * BM);
     p.grid_n = ceil_div(b_rows, gated ? BNH : BN);
     const long long total = (long long)p.grid_m * p.grid_n;
@@ -366,4 +379,11 @@ WICK_API int wick_gemm_tc2(const void* a, int a_rows, const void* b, long long b
     if (accumulate) return launch_pair<0, true, true>(map_a, map_b, p, 2 * pairs, smem, (cudaStream_t)stream);
     return out_f32 ? launch_pair<0, true, false>(map_a, map_b, p, 2 * pairs, smem, (cudaStream_t)stream)
                    : launch_pair<0, false, false>(map_a, map_b, p, 2 * pairs, smem, (cudaStream_t)stream);
+}
+
+WICK_API int wick_gemm_tc2(const void* a, int a_rows, const void* b, long long b_total_rows, int b_rows, int k, int gated,
+                           int pair_offset, int out_f32, int accumulate, int b_packed, void* out, long long ldo, int splits,
+                           long long split_stride, int* status, void* stream) {
+    return wick_gemm_tc2_grouped(a, a_rows, b, b_total_rows, b_rows, k, gated, pair_offset, out_f32, accumulate, b_packed, out, ldo,
+                                 splits, split_stride, nullptr, 0, status, stream);
 }

@@ -219,15 +219,19 @@ __global__ void moe_route_kernel(const int* __restrict__ tokens, const int* __re
 }
 
 __global__ void __launch_bounds__(1024)
-moe_place_kernel(const int* __restrict__ expert_of, const int* __restrict__ counts, int* __restrict__ row_of, int n_pairs) {
+moe_place_kernel(const int* __restrict__ expert_of, const int* __restrict__ counts, int* __restrict__ row_of, int n_pairs, int pad,
+                 int* __restrict__ expert_of_tile) {
     __shared__ int warp_count[32];
     pdl_trigger();
     pdl_wait();
     expert_of = fresh(expert_of);
     counts = fresh(counts);
     const int ex = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    // every expert's rows start at a multiple of `pad`; with a table of tiles (of `pad` rows), the expert's tiles are named
     int base = 0;
-    for (int e = 0; e < ex; ++e) base += counts[e];
+    for (int e = 0; e < ex; ++e) base += (counts[e] + pad - 1) / pad * pad;
+    if (expert_of_tile)
+        for (int tile = threadIdx.x; tile < (counts[ex] + pad - 1) / pad; tile += blockDim.x) expert_of_tile[base / pad + tile] = ex;
     // pairs in chunks of one per thread: a pair's row is the expert's first row plus the number of
     // the expert's pairs before it (earlier chunks, earlier warps of the chunk, earlier lanes of the warp)
     for (int i0 = 0; i0 < n_pairs; i0 += blockDim.x) {
@@ -278,6 +282,27 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
     row_of = fresh(row_of);
     base = fresh(base);
     const int t = blockIdx.x;
+    if ((width & 3) == 0 && (base_stride & 3) == 0) {
+        // four neighbours a thread; the rows' and the partial sums' loads are independent and issued together
+        for (int j = threadIdx.x * 4; j < width; j += blockDim.x * 4) {
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int c = 0; c < top; ++c) {
+                const int row = row_of ? row_of[t * top + c] : t * top + c;
+                if (row >= 0) {
+                    const float4 r = *reinterpret_cast<const float4*>(y + (int64_t)row * width + j);
+                    sum.x += r.x; sum.y += r.y; sum.z += r.z; sum.w += r.w;
+                }
+            }
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < base_splits; ++s) {
+                const float4 r = *reinterpret_cast<const float4*>(base + s * base_stride + (int64_t)t * width + j);
+                v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
+            }
+            *reinterpret_cast<float4*>(out + (int64_t)t * width + j) =
+                make_float4(v.x + weight * sum.x, v.y + weight * sum.y, v.z + weight * sum.z, v.w + weight * sum.w);
+        }
+        return;
+    }
     for (int j = threadIdx.x; j < width; j += blockDim.x) {
         float sum = 0.f;
         for (int c = 0; c < top; ++c) {
@@ -359,15 +384,18 @@ WICK_API int wick_moe_down_f32(const void* hidden, const int* tokens, const int*
 WICK_API int wick_moe_pairs_by_expert() { return PAIRS_BY_EXPERT; }
 
 // expert_of, row_of: int32 [n * top]; counts: int32 [experts], zero on entry.
+// pad: every expert's rows start at a multiple of it (1: no gaps); expert_of_tile: null, or int32 [enough tiles of
+// pad rows]: which expert a tile's rows belong to.
 WICK_API int wick_moe_route(const int* tokens, const int* table, int top, int n_experts, int* expert_of, int* counts,
-                            int* row_of, int n, void* s) {
+                            int* row_of, int n, int pad, int* expert_of_tile, void* s) {
+    WICK_REQUIRE(pad >= 1, "moe_route: bad padding");
     WICK_REQUIRE(top > 0 && n_experts > 0 && n >= 0, "moe_route: bad sizes");
     if (n == 0) return 0;
     const int pairs = n * top;
     WICK_CUDA(launch(moe_route_kernel, dim3(ceil_div(pairs, 256)), dim3(256), 0, (cudaStream_t)s, tokens, table, top, n_experts,
                      expert_of, counts, pairs));
     WICK_CUDA(launch(moe_place_kernel, dim3(n_experts), dim3(pairs >= 1024 ? 1024 : 256), 0, (cudaStream_t)s, (const int*)expert_of,
-                     (const int*)counts, row_of, pairs));
+                     (const int*)counts, row_of, pairs, pad, expert_of_tile));
     return check_launch("moe_route");
 }
 WICK_API int wick_moe_gather_bf16(const void* x, const int* row_of, int top, void* xs, int n, int width, void* s) {

@@ -716,10 +716,12 @@ def moe_table_down(hidden: torch.Tensor, tokens: torch.Tensor, table: torch.Tens
     return out
 
 
-def moe_route(tokens: torch.Tensor, table: torch.Tensor, n_experts: int) -> Tuple[torch.Tensor, torch.Tensor]:
+def moe_route(tokens: torch.Tensor, table: torch.Tensor, n_experts: int, pad: int = 1) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
     """The step's (token, choice) pairs sorted by expert: (counts int32 [experts], row_of int32
-    [n, top]): pair (t, c) is row ``row_of[t, c]`` of the sorted order, in which expert 0's pairs
-    come first and pairs of one expert keep their order (-1: the table names no expert)."""
+    [n, top], expert_of_tile): pair (t, c) is row ``row_of[t, c]`` of the sorted order, in which
+    expert 0's pairs come first and pairs of one expert keep their order (-1: the table names no
+    expert).  With ``pad`` > 1 every expert's rows start at a multiple of ``pad`` (the rows between
+    belong to nobody) and ``expert_of_tile`` int32 names the expert of every ``pad`` rows."""
     n = tokens.numel()
     _cuda("tokens", tokens, torch.int32, (n,))
     _cuda("table", table, torch.int32)
@@ -727,9 +729,10 @@ def moe_route(tokens: torch.Tensor, table: torch.Tensor, n_experts: int) -> Tupl
     counts = torch.zeros(n_experts, dtype=torch.int32, device=tokens.device)
     expert_of = torch.empty((n, top), dtype=torch.int32, device=tokens.device)
     row_of = torch.empty((n, top), dtype=torch.int32, device=tokens.device)
-    _layer().call("wick_moe_route", "ppiipppip", _p(tokens), _p(table), top, n_experts, _p(expert_of), _p(counts), _p(row_of),
-                  n, _stream(), kernels=2)
-    return counts, row_of
+    tiles = torch.zeros((n * top + pad - 1) // pad + n_experts, dtype=torch.int32, device=tokens.device) if pad > 1 else None
+    _layer().call("wick_moe_route", "ppiipppiipp", _p(tokens), _p(table), top, n_experts, _p(expert_of), _p(counts), _p(row_of),
+                  n, int(pad), _p(tiles), _stream(), kernels=2)
+    return counts, row_of, tiles
 
 
 def moe_gather(x: torch.Tensor, row_of: torch.Tensor, n_rows: int) -> torch.Tensor:
@@ -738,7 +741,7 @@ def moe_gather(x: torch.Tensor, row_of: torch.Tensor, n_rows: int) -> torch.Tens
     n, width = x.shape
     _cuda("row_of", row_of, torch.int32)
     top = row_of.shape[1]
-    xs = torch.empty((n_rows, width), dtype=x.dtype, device=x.device)
+    xs = torch.zeros((n_rows, width), dtype=x.dtype, device=x.device)      # (rows between the experts' stay zero)
     _layer().call(f"wick_moe_gather_{_dt(x)}", "ppipiip", _p(x), _p(row_of), top, _p(xs), n, width, _stream())
     return xs
 

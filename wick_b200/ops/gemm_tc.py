@@ -124,10 +124,14 @@ def unpack(packed: torch.Tensor, rows: int, k: int, gated: bool = False) -> torc
 
 def gemm_tc_pair(a: torch.Tensor, b: torch.Tensor, b_rows: int, *, out: torch.Tensor, ldo: int, gated: bool = False,
                  pair_offset: int = 0, accumulate: bool = False, b_packed: bool = False, splits: int = 1,
-                 split_stride: int = 0) -> None:
+                 split_stride: int = 0, groups: Optional[torch.Tensor] = None, group_rows: int = 0) -> None:
     """The kernel for pairs of thread blocks (see ``wick_gemm_tc2`` in gemm_tc2.cu): out[m, n] = a[m] . b[n],
     or out[m, n] += ... with ``accumulate`` (float32 output), or ``splits`` partial sums over runs of the inner
-    dimension, ``split_stride`` elements apart (float32 output)."""
+    dimension, ``split_stride`` elements apart (float32 output).  ``groups`` (int32 on the device, one entry per
+    256 rows of ``a``): ``b`` holds several matrices of ``group_rows`` rows one after the other, and rows
+    256 i .. of ``a`` are multiplied with matrix ``groups[i]``."""
+    if groups is not None and (groups.dtype != torch.int32 or not groups.is_cuda or groups.numel() < (a.shape[0] + 255) // 256):
+        raise KernelError("gemm_tc_pair: groups must be int32 on the device, one entry per 256 rows of a")
     for nm, t in (("a", a), ("b", b)):
         if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous()):
             raise KernelError(f"gemm_tc_pair: {nm} must be a contiguous bfloat16 CUDA tensor")
@@ -140,9 +144,10 @@ def gemm_tc_pair(a: torch.Tensor, b: torch.Tensor, b_rows: int, *, out: torch.Te
     if out.dtype not in (torch.float32, torch.bfloat16) or not out.is_contiguous():
         raise KernelError("gemm_tc_pair: out must be contiguous float32 or bfloat16")
     st = status_tensor(a.device)
-    _lib().call("wick_gemm_tc2", "pipliiiiiiiplilpp", _p(a), a.shape[0], _p(b), b.shape[0] * 128 if b_packed else b.shape[0],
+    _lib().call("wick_gemm_tc2_grouped", "pipliiiiiiiplilpipp", _p(a), a.shape[0], _p(b), b.shape[0] * 128 if b_packed else b.shape[0],
                 b_rows, a.shape[1], 1 if gated else 0, pair_offset, 1 if out.dtype == torch.float32 else 0,
-                1 if accumulate else 0, 1 if b_packed else 0, _p(out), ldo, splits, split_stride, _p(st), _stream())
+                1 if accumulate else 0, 1 if b_packed else 0, _p(out), ldo, splits, split_stride, _p(groups), int(group_rows),
+                _p(st), _stream())
 
 
 def _ceil16(n: int) -> int:

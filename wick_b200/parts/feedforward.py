@@ -22,7 +22,7 @@ the shared part's.
 """
 from __future__ import annotations
 
-from typing import List, Optional
+from typing import Optional
 
 import numpy as np
 import torch
@@ -30,17 +30,6 @@ import torch
 from .. import ops
 from .base import FeedForward, TensorSpec, build_part, register_part
 from .linear import Linear
-
-
-_streams = {}
-
-
-def _side_streams(device, n: int = 4):
-    """A few streams per device for work that a step forks and joins."""
-    key = torch.device(device)
-    if key not in _streams:
-        _streams[key] = [torch.cuda.Stream(device=key) for _ in range(n)]
-    return _streams[key]
 
 
 class NoFeedForward(FeedForward):
@@ -109,9 +98,8 @@ class TableMoE(FeedForward):
         self.gate_up: Optional[torch.Tensor] = None      # [experts, 2, intermediate, width]
         self.down: Optional[torch.Tensor] = None         # [experts, width, intermediate]
         self.table: Optional[torch.Tensor] = None        # int32 [vocab, top]
-        # The same matrices once more, one tensor-core plan per expert, for steps of many tokens (bfloat16).
-        self.expert_up: List[Linear] = []
-        self.expert_down: List[Linear] = []
+        self.up_tiles: Optional[torch.Tensor] = None     # the experts' gate/up and down matrices as tiles (bfloat16)
+        self.down_tiles: Optional[torch.Tensor] = None
 
     def _expert(self, i: int, which: str) -> str:
         return self.names["expert"].format(i=i) + self.names[which]
@@ -141,18 +129,15 @@ class TableMoE(FeedForward):
             raise ValueError(f"the expert table names expert {lo if lo < 0 else hi}; there are {self.experts}")
         if self.shared is not None:
             self.shared.load(lambda n: fetch(self.names["shared"] + n))
-        self.expert_up, self.expert_down = [], []
-        if self.ctx.dtype == torch.bfloat16 and self.gate_up.is_cuda and not ops.plain_kernels():
-            for i in range(self.experts):
-                up = Linear(2 * self.intermediate, self.width, self.ctx, gated=True)
-                up.use(self.gate_up[i].reshape(2 * self.intermediate, self.width))
-                down = Linear(self.width, self.intermediate, self.ctx)
-                down.use(self.down[i])
-                if up._tensor_core() is None or down._tensor_core() is None:
-                    self.expert_up, self.expert_down = [], []
-                    break
-                self.expert_up.append(up)
-                self.expert_down.append(down)
+        # The same matrices once more, as tiles for the tensor-core product of steps with many tokens
+        # (bfloat16; rows of 16-byte multiples): all experts one after the other in one operand.
+        self.up_tiles = self.down_tiles = None
+        if (self.ctx.dtype == torch.bfloat16 and self.gate_up.is_cuda and not ops.plain_kernels()
+                and self.width % 8 == 0 and self.intermediate % 8 == 0):
+            from ..ops import gemm_tc
+            self.up_tiles = torch.cat([gemm_tc.pack(self.gate_up[i].reshape(2 * self.intermediate, self.width), gated=True)
+                                       for i in range(self.experts)], 0)
+            self.down_tiles = torch.cat([gemm_tc.pack(self.down[i]) for i in range(self.experts)], 0)
 
     def tensor(self, name):
         for i in range(self.experts):
@@ -184,52 +169,40 @@ class TableMoE(FeedForward):
             if base.dim() == 2:
                 base = base.unsqueeze(0)
         n = x.shape[0]
-        if self.expert_up and n >= self.SORTED_FROM and not torch.cuda.is_current_stream_capturing():
+        if self.up_tiles is not None and n >= self.SORTED_FROM and not torch.cuda.is_current_stream_capturing():
             return self._forward_sorted(x, batch, base)
         hidden = ops.moe_table_up(x, batch.tokens, self.table, self.gate_up)
         return ops.moe_table_down(hidden, batch.tokens, self.table, self.down, 1.0 / self.top, base).unsqueeze(0)
 
-    # From this many tokens on a step (that is not being captured) sorts its rows by expert and
-    # runs every expert's rows through the tensor-core products.  The host has to know the experts'
-    # row counts for that: it counts them itself from the step's token ids where the step's
-    # description has them (the table is a constant), and otherwise reads the device's counts
-    # (one wait per layer).  Fewer tokens go through the kernels that walk the matrices by expert.
+    # From this many tokens on a step (that is not being captured) sorts its rows by expert, every
+    # expert's rows starting at a multiple of 256, and runs ONE tensor-core product over all of
+    # them: a tile of 256 rows is multiplied with the matrices of the expert the tile belongs to.
+    # The host has to know how many rows that makes: it counts them itself from the step's token
+    # ids where the step's description has them (the table is a constant), and otherwise reads the
+    # device's counts (one wait per layer).  Fewer tokens go through the kernels that walk the
+    # matrices by expert.
     SORTED_FROM = 64
-    ONE_STREAM_FROM = 1 << 16      # rows (over all experts) from which every expert fills the part alone
+    ROW_TILE = 256
 
     def _forward_sorted(self, x, batch, base):
-        n, dt = x.shape[0], self.ctx.dtype
-        counts, row_of = ops.moe_route(batch.tokens, self.table, self.experts)
+        from ..ops import gemm_tc
+        n, dt, pad = x.shape[0], self.ctx.dtype, self.ROW_TILE
+        counts, row_of, tiles = ops.moe_route(batch.tokens, self.table, self.experts, pad=pad)
         host = getattr(batch, "host", None)
         if host is not None:
             ids = host[batch.layout.tokens:batch.layout.tokens + n]
             counts = np.bincount(self.table_host[ids].ravel(), minlength=self.experts).tolist()
         else:
             counts = counts.tolist()                        # (the host waits here)
-        rows = sum(counts)
+        rows = sum((c + pad - 1) // pad * pad for c in counts)
+        f, w = self.intermediate, self.width
+        f_pad, w_pad = (f + 127) // 128 * 128, (w + 127) // 128 * 128
         xs = ops.moe_gather(x, row_of, rows)
-        hidden = torch.empty((rows, self.intermediate), dtype=dt, device=x.device)
-        y = torch.empty((rows, self.width), dtype=torch.float32, device=x.device)
-        # An expert's few hundred rows make fewer tiles than the part has multiprocessors, so the experts'
-        # products go to several streams and run side by side; the step's stream waits for all of them.
-        main = torch.cuda.current_stream()
-        side = _side_streams(x.device)
-        fork = torch.cuda.Event()
-        fork.record(main)
-        at, used = 0, []
-        for i, c in enumerate(counts):
-            if c:
-                st = side[len(used) % len(side)] if rows < self.ONE_STREAM_FROM else main
-                if st is not main and st not in used:
-                    st.wait_event(fork)
-                with torch.cuda.stream(st), ops.stream_scope():
-                    self.expert_up[i]._tensor_core()._run(xs[at:at + c], hidden[at:at + c], 1)
-                    self.expert_down[i]._tensor_core()._run(hidden[at:at + c], y[at:at + c], 1)
-                if st is not main:
-                    used.append(st)
-                at += c
-        for st in set(used):
-            main.wait_stream(st)
+        hidden = torch.empty((rows, f), dtype=dt, device=x.device)
+        y = torch.empty((rows, w), dtype=torch.float32, device=x.device)
+        gemm_tc.gemm_tc_pair(xs, self.up_tiles, f, out=hidden, ldo=f, gated=True, pair_offset=f_pad, b_packed=True,
+                             groups=tiles, group_rows=2 * f_pad)
+        gemm_tc.gemm_tc_pair(hidden, self.down_tiles, w, out=y, ldo=w, b_packed=True, groups=tiles, group_rows=w_pad)
         return ops.moe_combine(y, row_of, 1.0 / self.top, base).unsqueeze(0)
 
 
