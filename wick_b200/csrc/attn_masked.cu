@@ -209,11 +209,17 @@ attn_masked_kernel(const T* __restrict__ q, const T* __restrict__ kv, T* __restr
             const T* kp = kv + (j / kPage == first_page ? page_a : page_b) + ((int64_t)g * kPage + (j % kPage)) * d;
             float dot = 0.f;
             if (k_vec) {
-                for (int x = 0; x < d; x += VN) {
-                    Vec16<T> kk;
-                    kk.load(kp + x);
+                for (int x = 0; x < d; x += 4 * VN) {            // four loads of 16 bytes in flight
+                    Vec16<T> kk[4];
 #pragma unroll
-                    for (int i = 0; i < VN; ++i) dot = fmaf(qs[x + i], kk.v[i], dot);
+                    for (int u = 0; u < 4; ++u)
+                        if (x + u * VN < d) kk[u].load(kp + x + u * VN);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (x + u * VN < d) {
+#pragma unroll
+                            for (int i = 0; i < VN; ++i) dot = fmaf(qs[x + u * VN + i], kk[u].v[i], dot);
+                        }
                 }
             } else {
                 for (int x = 0; x < d; ++x) dot = fmaf(qs[x], ld(kp + x), dot);

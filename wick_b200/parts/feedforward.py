@@ -169,19 +169,19 @@ class TableMoE(FeedForward):
             if base.dim() == 2:
                 base = base.unsqueeze(0)
         n = x.shape[0]
-        if self.up_tiles is not None and n >= self.SORTED_FROM and not torch.cuda.is_current_stream_capturing():
+        if self.up_tiles is not None and n >= self.SORTED_FROM:
             return self._forward_sorted(x, batch, base)
         hidden = ops.moe_table_up(x, batch.tokens, self.table, self.gate_up)
         return ops.moe_table_down(hidden, batch.tokens, self.table, self.down, 1.0 / self.top, base).unsqueeze(0)
 
-    # From this many tokens on a step (that is not being captured) sorts its rows by expert, every
-    # expert's rows starting at a multiple of 256, and runs ONE tensor-core product over all of
-    # them: a tile of 256 rows is multiplied with the matrices of the expert the tile belongs to.
-    # The host has to know how many rows that makes: it counts them itself from the step's token
-    # ids where the step's description has them (the table is a constant), and otherwise reads the
-    # device's counts (one wait per layer).  Fewer tokens go through the kernels that walk the
-    # matrices by expert.
-    SORTED_FROM = 64
+    # From this many tokens on a step sorts its rows by expert, every expert's rows starting at a
+    # multiple of 256, and runs ONE tensor-core product over all of them: a tile of 256 rows is
+    # multiplied with the matrices of the expert the tile belongs to.  How many rows that makes
+    # depends on the step's tokens: the host counts them from the step's token ids where the step's
+    # description has them (the table is a constant); otherwise (a captured step, whose tokens the
+    # host never sees) the product runs over the most rows there can be, and the tiles beyond the
+    # last expert's hold zeros.  Fewer tokens go through the kernels that walk the matrices by expert.
+    SORTED_FROM = 16
     ROW_TILE = 256
 
     def _forward_sorted(self, x, batch, base):
@@ -189,12 +189,12 @@ class TableMoE(FeedForward):
         n, dt, pad = x.shape[0], self.ctx.dtype, self.ROW_TILE
         counts, row_of, tiles = ops.moe_route(batch.tokens, self.table, self.experts, pad=pad)
         host = getattr(batch, "host", None)
-        if host is not None:
+        if host is not None and not torch.cuda.is_current_stream_capturing():
             ids = host[batch.layout.tokens:batch.layout.tokens + n]
-            counts = np.bincount(self.table_host[ids].ravel(), minlength=self.experts).tolist()
+            counts = np.bincount(self.table_host[ids].ravel(), minlength=self.experts)
+            rows = int(((counts + pad - 1) // pad * pad).sum())
         else:
-            counts = counts.tolist()                        # (the host waits here)
-        rows = sum((c + pad - 1) // pad * pad for c in counts)
+            rows = min(self.experts, n * self.top) * pad + (n * self.top) // pad * pad
         f, w = self.intermediate, self.width
         f_pad, w_pad = (f + 127) // 128 * 128, (w + 127) // 128 * 128
         xs = ops.moe_gather(x, row_of, rows)
