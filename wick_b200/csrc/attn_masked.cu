@@ -7,7 +7,7 @@
 //
 //   finish  : the q/k/v projection's float32 partial sums -> q (activation type) and the
 //             token's key and value in its sequence's cache page
-//   attend  : every new token over the cache, one block per (token, query head)
+//   attend  : every new token over the cache, one block per (token, query head) or per (token, key/value head)
 //
 // Cache page of one schedule entry: [kv_head][64][d] keys, then [kv_head][64][e] values.
 // Scores, the softmax, its weights and the weighted sum are float32.  A token's work is the
@@ -152,8 +152,9 @@ qkv_finish_kernel(const float* __restrict__ parts, int splits, int64_t split_str
 // j0 + l (a dot product of d numbers, in index order), the warp's running maximum and sum
 // follow, then every lane adds the 32 weighted value rows into its own elements of the result.
 // At the end the warps' partial results are folded in warp order; a sink joins there as a
-// score without a value.  The number of warps is chosen by the step's size (few tokens: 8,
-// so that a decode step keeps the part busy; many: 1), which changes the order of sums only.
+// score without a value.  This form runs with one warp a block, for steps of many tokens (the
+// 32-bit path's prompts, and the twin of the tensor-core kernel); steps of few tokens take the
+// grouped form below, which changes the order of sums only.
 constexpr int E_CHUNKS = 2;                    // value sizes up to 256: a lane holds 4 neighbours of every 128
 
 __device__ __forceinline__ void load4(const float* p, float* v) {
@@ -295,6 +296,178 @@ attn_masked_kernel(const T* __restrict__ q, const T* __restrict__ kv, T* __restr
         }
 }
 
+// ---------------------------------------------------------------------------
+// The form for steps of few tokens (a decode step): one block per (token, key/value head); its
+// warps share the visible keys, 32 at a time, and every key and value row is read ONCE, by a whole
+// warp (a lane holds the elements 4 l .. 4 l + 3 of every 128), for up to RH query heads of the
+// group together: the lanes' partial products are added by the butterfly, lane j keeps key j's
+// score of each head, the running maxima and sums follow per head, and every lane adds the weighted
+// value rows into its own elements of each head's result.  The warps' partial results are folded
+// in warp order (warp r folds head r); a sink joins there.  Groups of more than RH heads take
+// several passes over the keys.
+template <typename T, int RH>
+__global__ void __launch_bounds__(256)
+attn_masked_group_kernel(const T* __restrict__ q, const T* __restrict__ kv, T* __restrict__ out,
+                         const int* __restrict__ seq_of_token, const int* __restrict__ positions,
+                         const int* __restrict__ page_table, int table_width, int H, int G, int d, int e,
+                         float scale, int mask, int mask_size, const float* __restrict__ sink) {
+    extern __shared__ float smem[];
+    pdl_trigger();
+    pdl_wait();
+    q = fresh(q);
+    kv = fresh(kv);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int g = blockIdx.x, t = blockIdx.y, R = H / G;
+    const int pos = positions[t];
+    const int* table = page_table + (int64_t)seq_of_token[t] * table_width;
+    constexpr int e_pad = 128 * E_CHUNKS;
+    float* ms = smem;                               // [warps][RH] maxima, then [warps][RH] sums
+    float* accs = ms + 2 * n_warps * RH;            // [warps][RH][e_pad]
+    const int64_t page_elems = (int64_t)G * kPage * (d + e);
+    const int64_t v_off = (int64_t)G * kPage * d;
+    const bool aligned = (((uintptr_t)kv) & 15) == 0 && (page_elems * sizeof(T)) % 16 == 0 && (v_off * sizeof(T)) % 16 == 0;
+    const bool k_vec = d % 4 == 0 && aligned, v_vec = e % 4 == 0 && aligned;
+    const int lo = first_visible(pos, mask, mask_size);
+    for (int r0 = 0; r0 < R; r0 += RH) {
+        // this pass's query rows, the lane's elements of each
+        float qr[RH][4 * E_CHUNKS];
+#pragma unroll
+        for (int r = 0; r < RH; ++r)
+#pragma unroll
+            for (int c = 0; c < E_CHUNKS; ++c)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int x = 128 * c + 4 * lane + i;
+                    qr[r][4 * c + i] = (r0 + r < R && x < d) ? ld(q + ((int64_t)t * H + g * R + r0 + r) * d + x) : 0.f;
+                }
+        float m[RH], l[RH], acc[RH][4 * E_CHUNKS];
+#pragma unroll
+        for (int r = 0; r < RH; ++r) {
+            m[r] = -INFINITY;
+            l[r] = 0.f;
+#pragma unroll
+            for (int c = 0; c < 4 * E_CHUNKS; ++c) acc[r][c] = 0.f;
+        }
+        for (int j0 = lo + 32 * warp; j0 <= pos; j0 += 32 * n_warps) {
+            const int first_page = j0 / kPage;
+            const int64_t page_a = table[first_page] * page_elems;
+            const int64_t page_b = (first_page + 1) * kPage <= min(pos, j0 + 31) ? table[first_page + 1] * page_elems : page_a;
+            const int n_keys = min(32, pos - j0 + 1);
+            float sc[RH];
+#pragma unroll
+            for (int r = 0; r < RH; ++r) sc[r] = -INFINITY;
+            auto score = [&](int jj) {
+                const int key = j0 + jj;
+                const T* kp = kv + (key / kPage == first_page ? page_a : page_b) + ((int64_t)g * kPage + (key % kPage)) * d;
+                float kk[4 * E_CHUNKS];
+#pragma unroll
+                for (int c = 0; c < E_CHUNKS; ++c) {
+                    const int x = 128 * c + 4 * lane;
+                    if (k_vec) {
+                        if (x < d) load4(kp + x, kk + 4 * c);
+                        else kk[4 * c] = kk[4 * c + 1] = kk[4 * c + 2] = kk[4 * c + 3] = 0.f;
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) kk[4 * c + i] = x + i < d ? ld(kp + x + i) : 0.f;
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < RH; ++r) {
+                    float part = 0.f;
+#pragma unroll
+                    for (int c = 0; c < 4 * E_CHUNKS; ++c) part = fmaf(qr[r][c], kk[c], part);
+                    part = warp_sum(part);
+                    if (lane == jj) sc[r] = part * scale;
+                }
+            };
+            if (n_keys == 32) {
+#pragma unroll 8
+                for (int jj = 0; jj < 32; ++jj) score(jj);
+            } else {
+                for (int jj = 0; jj < n_keys; ++jj) score(jj);
+            }
+            float p[RH];
+#pragma unroll
+            for (int r = 0; r < RH; ++r) {
+                const float m_new = fmaxf(m[r], warp_max(sc[r]));      // finite: key j0 is visible
+                const float corr = expf(m[r] - m_new);                 // (-inf at first: 0)
+                p[r] = lane < n_keys ? expf(sc[r] - m_new) : 0.f;
+                l[r] = l[r] * corr + warp_sum(p[r]);
+                m[r] = m_new;
+#pragma unroll
+                for (int c = 0; c < 4 * E_CHUNKS; ++c) acc[r][c] *= corr;
+            }
+            auto add_value = [&](int jj) {
+                const int key = j0 + jj;
+                const T* vp = kv + (key / kPage == first_page ? page_a : page_b) + v_off + ((int64_t)g * kPage + (key % kPage)) * e;
+                float vv[4 * E_CHUNKS];
+#pragma unroll
+                for (int c = 0; c < E_CHUNKS; ++c) {
+                    const int x = 128 * c + 4 * lane;
+                    if (v_vec) {
+                        if (x < e) load4(vp + x, vv + 4 * c);
+                        else vv[4 * c] = vv[4 * c + 1] = vv[4 * c + 2] = vv[4 * c + 3] = 0.f;
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) vv[4 * c + i] = x + i < e ? ld(vp + x + i) : 0.f;
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < RH; ++r) {
+                    const float pj = __shfl_sync(0xffffffffu, p[r], jj);
+#pragma unroll
+                    for (int c = 0; c < 4 * E_CHUNKS; ++c) acc[r][c] = fmaf(pj, vv[c], acc[r][c]);
+                }
+            };
+            if (n_keys == 32) {
+#pragma unroll 8
+                for (int jj = 0; jj < 32; ++jj) add_value(jj);
+            } else {
+                for (int jj = 0; jj < n_keys; ++jj) add_value(jj);
+            }
+        }
+        __syncthreads();                                   // (the pass before is folded)
+#pragma unroll
+        for (int r = 0; r < RH; ++r) {
+            if (lane == 0) {
+                ms[warp * RH + r] = m[r];
+                ms[(n_warps + warp) * RH + r] = l[r];
+            }
+#pragma unroll
+            for (int c = 0; c < E_CHUNKS; ++c)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) accs[((int64_t)warp * RH + r) * e_pad + 128 * c + 4 * lane + i] = acc[r][4 * c + i];
+        }
+        __syncthreads();
+        for (int r = warp; r < RH && r0 + r < R; r += n_warps) {
+            const int h = g * R + r0 + r;
+            float big = sink ? sink[h] : -INFINITY;
+            for (int w = 0; w < n_warps; ++w) big = fmaxf(big, ms[w * RH + r]);     // finite: warp 0 holds the first visible key
+            float total = sink ? expf(sink[h] - big) : 0.f;
+            float o[4 * E_CHUNKS];
+#pragma unroll
+            for (int c = 0; c < 4 * E_CHUNKS; ++c) o[c] = 0.f;
+            for (int w = 0; w < n_warps; ++w) {
+                const float mw = ms[w * RH + r];
+                const float f = mw == -INFINITY ? 0.f : expf(mw - big);
+                total += ms[(n_warps + w) * RH + r] * f;
+#pragma unroll
+                for (int c = 0; c < E_CHUNKS; ++c)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) o[4 * c + i] = fmaf(accs[((int64_t)w * RH + r) * e_pad + 128 * c + 4 * lane + i], f, o[4 * c + i]);
+            }
+            const float inv = 1.0f / total;
+#pragma unroll
+            for (int c = 0; c < E_CHUNKS; ++c)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int x = 128 * c + 4 * lane + i;
+                    if (x < e) st(out + ((int64_t)t * H + h) * e + x, o[4 * c + i] * inv);
+                }
+        }
+    }
+}
+
 template <typename T>
 int qkv_finish(const float* parts, int splits, int n, const float* bias, int H, int G, int d, int e, const float* q_w,
                int q_span, const float* k_w, int k_span, float eps, const float* cos_t, const float* sin_t, int rot_dims,
@@ -332,7 +505,22 @@ int attn_masked(const void* q, const void* kv, void* out, const int* seq_of_toke
     WICK_REQUIRE(e <= 128 * E_CHUNKS, "attn_masked: a value size of %d is beyond %d", e, 128 * E_CHUNKS);
     WICK_REQUIRE(mask == MASK_CAUSAL || mask_size > 0, "attn_masked: the mask needs a positive size");
     if (n == 0) return 0;
-    const int warps = (int64_t)n * H <= 8192 ? 8 : 1;
+    if ((int64_t)n * H <= 8192 && d <= 128 * E_CHUNKS && n <= 65535) {
+        // few tokens: a block per (token, key/value head), rows read once for the group's query heads
+        const int R = H / G, warps = 8;
+        const int rh = R >= 4 ? 4 : (R >= 2 ? 2 : 1);
+        const size_t smem_g = (size_t)(2 * warps * rh + warps * rh * 128 * E_CHUNKS) * sizeof(float);
+        const dim3 grid(G, n), block(warps * 32);
+#define WICK_GROUP(RH)                                                                                                          \
+        WICK_CUDA(launch(attn_masked_group_kernel<T, RH>, grid, block, smem_g, s, (const T*)q, (const T*)kv, (T*)out, seq_of_token, \
+                         positions, page_table, table_width, H, G, d, e, scale, mask, mask_size, sink))
+        if (rh == 4) WICK_GROUP(4);
+        else if (rh == 2) WICK_GROUP(2);
+        else WICK_GROUP(1);
+#undef WICK_GROUP
+        return check_launch("attn_masked");
+    }
+    const int warps = 1;
     const size_t smem = (size_t)(((d + 3) & ~3) + 2 * warps + warps * 128 * E_CHUNKS) * sizeof(float);
     WICK_REQUIRE(smem <= 48 * 1024, "attn_masked: a head size of %d is beyond one block's shared memory", d);
     WICK_CUDA(launch(attn_masked_kernel<T>, dim3((unsigned)((int64_t)n * H)), dim3(warps * 32), smem, s, (const T*)q,
