@@ -310,14 +310,15 @@ __global__ void __launch_bounds__(256)
 attn_masked_group_kernel(const T* __restrict__ q, const T* __restrict__ kv, T* __restrict__ out,
                          const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                          const int* __restrict__ page_table, int table_width, int H, int G, int d, int e,
-                         float scale, int mask, int mask_size, const float* __restrict__ sink) {
+                         float scale, int mask, int mask_size, const float* __restrict__ sink, int heads_per_block) {
     extern __shared__ float smem[];
     pdl_trigger();
     pdl_wait();
     q = fresh(q);
     kv = fresh(kv);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
-    const int g = blockIdx.x, t = blockIdx.y, R = H / G;
+    // the block's query heads h0 .. h0 + R - 1 lie in one group (heads_per_block divides the group's size)
+    const int t = blockIdx.y, R = heads_per_block, h0 = blockIdx.x * heads_per_block, g = h0 / (H / G);
     const int pos = positions[t];
     const int* table = page_table + (int64_t)seq_of_token[t] * table_width;
     constexpr int e_pad = 128 * E_CHUNKS;
@@ -338,7 +339,7 @@ attn_masked_group_kernel(const T* __restrict__ q, const T* __restrict__ kv, T* _
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int x = 128 * c + 4 * lane + i;
-                    qr[r][4 * c + i] = (r0 + r < R && x < d) ? ld(q + ((int64_t)t * H + g * R + r0 + r) * d + x) : 0.f;
+                    qr[r][4 * c + i] = (r0 + r < R && x < d) ? ld(q + ((int64_t)t * H + h0 + r0 + r) * d + x) : 0.f;
                 }
         float m[RH], l[RH], acc[RH][4 * E_CHUNKS];
 #pragma unroll
@@ -440,7 +441,7 @@ attn_masked_group_kernel(const T* __restrict__ q, const T* __restrict__ kv, T* _
         }
         __syncthreads();
         for (int r = warp; r < RH && r0 + r < R; r += n_warps) {
-            const int h = g * R + r0 + r;
+            const int h = h0 + r0 + r;
             float big = sink ? sink[h] : -INFINITY;
             for (int w = 0; w < n_warps; ++w) big = fmaxf(big, ms[w * RH + r]);     // finite: warp 0 holds the first visible key
             float total = sink ? expf(sink[h] - big) : 0.f;
@@ -507,13 +508,17 @@ int attn_masked(const void* q, const void* kv, void* out, const int* seq_of_toke
     if (n == 0) return 0;
     if ((int64_t)n * H <= 8192 && d <= 128 * E_CHUNKS && n <= 65535) {
         // few tokens: a block per (token, key/value head), rows read once for the group's query heads
-        const int R = H / G, warps = 8;
-        const int rh = R >= 4 ? 4 : (R >= 2 ? 2 : 1);
+        // With few blocks the group's heads are spread over several blocks (each reads the rows again, from the L2 cache).
+        int hpb = H / G;
+        const int warps = 8;
+        while (hpb % 2 == 0 && (int64_t)(H / hpb) * n < 148) hpb /= 2;
+        if (hpb > 1 && (int64_t)(H / hpb) * n < 148) hpb = 1;
+        const int rh = hpb >= 4 ? 4 : (hpb >= 2 ? 2 : 1);
         const size_t smem_g = (size_t)(2 * warps * rh + warps * rh * 128 * E_CHUNKS) * sizeof(float);
-        const dim3 grid(G, n), block(warps * 32);
+        const dim3 grid(H / hpb, n), block(warps * 32);
 #define WICK_GROUP(RH)                                                                                                          \
         WICK_CUDA(launch(attn_masked_group_kernel<T, RH>, grid, block, smem_g, s, (const T*)q, (const T*)kv, (T*)out, seq_of_token, \
-                         positions, page_table, table_width, H, G, d, e, scale, mask, mask_size, sink))
+                         positions, page_table, table_width, H, G, d, e, scale, mask, mask_size, sink, hpb))
         if (rh == 4) WICK_GROUP(4);
         else if (rh == 2) WICK_GROUP(2);
         else WICK_GROUP(1);
