@@ -269,6 +269,36 @@ def test_tensor_core_prompt_attention_equals_the_warp_kernel(mask, size, d, H, G
         assert (out.float() - ref.float()).abs().max().item() < 0.03, (mask, size, d, sk is None)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("mask,size", [("block", 50), ("block", 300), ("window", 37), ("causal", 0)])
+@pytest.mark.parametrize("d,H,G", [(16, 4, 4), (48, 6, 1), (128, 8, 2)])
+def test_bulk_copy_decode_attention_equals_the_warp_kernel(mask, size, d, H, G, dtype):
+    """One token for each of four sequences of different lengths (one of them a single position, one that ends
+    on a page's and a block's first position), pages in no order."""
+    g = torch.Generator().manual_seed(9)
+    lens = [1, 301, 129, 600]
+    pages = [[3], [5, 2, 8, 11, 4], [1, 9, 12], [6, 7, 10, 13, 14, 15, 16, 17, 18, 19]]
+    kv = torch.full((20, 2 * G * PAGE * d), float("nan"))
+    for b, n in enumerate(lens):
+        one = fill_cache(torch.randn(n, G, d, generator=g), torch.randn(n, G, d, generator=g), pages[b], 20)
+        for pg in pages[b][:(n + PAGE - 1) // PAGE]:
+            kv[pg] = one[pg]
+    kv = kv.to(dtype).to(DEV)
+    q = torch.randn(4, H, d, generator=g).to(dtype).to(DEV)
+    sink = torch.randn(H, generator=g).to(DEV)
+    lay = BatchLayout(4, 4, 10, 0)
+    host = np.zeros(lay.size, dtype=np.int32)
+    fill_host(lay, host, tokens=[[0]] * 4, starts=[n - 1 for n in lens], slots=[1, 2, 3, 4], pages=pages, want=[[]] * 4)
+    batch = StepBatch(lay, torch.from_numpy(host).to(DEV), q_lens=[1] * 4, starts=[n - 1 for n in lens])
+    assert batch.is_decode and ops.attention_masked_kind(d, d, dtype, True) == "bulk"
+    for sk in (sink, None):
+        kw = dict(n_kv=G, v_dim=d, mask=mask, mask_size=size, sink=sk)
+        ref = ops.attention_masked(q, kv, batch, 0.2, kind="warp", **kw)
+        out = ops.attention_masked(q, kv, batch, 0.2, kind="bulk", **kw)
+        assert torch.isfinite(out.float()).all()
+        assert (out.float() - ref.float()).abs().max().item() < (2e-5 if dtype == torch.float32 else 0.02), (mask, size, d)
+
+
 @pytest.mark.parametrize("size", [50, 64])
 def test_one_key_that_stands_out_shows_on_which_side_of_an_edge_it_lies(size):
     """Key j is made to dominate every query that sees it (its score is far above all others) and its value is

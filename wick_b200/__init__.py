@@ -1,7 +1,7 @@
 """wick_b200: a small model library with generation for one NVIDIA B200.
 
 Everything between a request's token ids and its next token for the Qwen3 dense
-decoder: typed configuration and architecture registry, safetensors weights (or
+decoder and the Nibotar decoder: typed configuration and architecture registry, safetensors weights (or
 seeded random ones), layers assembled from registered parts, a paged cache with
 a slot per sequence, one step function for batches of unequal sequences, a
 generation loop, sampling, and hand-written CUDA kernels for sm_100a.

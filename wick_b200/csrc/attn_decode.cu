@@ -26,6 +26,12 @@ namespace fastdecode {
 constexpr int HD = WICK_HD;
 constexpr int GT = 4;                                  // query heads handled per pass
 
+// First key that the query at position p sees: mask 0 every earlier key, 1 those of p's own block of `size`
+// positions (blocks counted from position 0), 2 the last `size` positions.
+__device__ __forceinline__ int first_visible_key(int p, int mask, int size) {
+    return mask == 1 ? p / size * size : (mask == 2 ? max(0, p - size + 1) : 0);
+}
+
 template <typename T> struct Shape {
     static constexpr int EPC = Vec16<T>::N;                      // elements per 16-byte chunk
     static constexpr int CHUNKS = HD / EPC;                      // chunks per row
@@ -47,7 +53,7 @@ __global__ void __launch_bounds__(Shape<T>::THREADS)
 attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ kv, float* __restrict__ part_o,
                         float* __restrict__ part_ml, const int* __restrict__ kv_len_arr,
                         const int* __restrict__ page_table, int table_width, int n_heads, int n_kv, int max_splits,
-                        float scale, int* status) {
+                        float scale, int* status, int mask, int mask_size) {
     using S = Shape<T>;
     constexpr int EPC = S::EPC, CHUNKS = S::CHUNKS, WARPS = S::WARPS, SPLIT = S::SPLIT, THREADS = S::THREADS;
     constexpr int TS = S::TS, CPL = S::CPL, KPI = S::KPI;
@@ -66,6 +72,9 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ kv, float
     }
     const int key_begin = split * SPLIT;
     if (key_begin >= kv_len) return;
+    // the new token (position kv_len - 1) sees the keys from key_lo on; a split that lies before them has no part
+    const int key_lo = first_visible_key(kv_len - 1, mask, mask_size);
+    if (key_begin + SPLIT <= key_lo) return;
     const int group = n_heads / n_kv;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
@@ -147,7 +156,7 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ kv, float
 #pragma unroll
         for (int kk = 0; kk < 2; ++kk) {
             const int key = lane + 32 * kk;
-            const bool valid = warp_live && key_begin + warp * kPage + key < kv_len;
+            const bool valid = warp_live && key_begin + warp * kPage + key < kv_len && key_begin + warp * kPage + key >= key_lo;
 #pragma unroll
             for (int h = 0; h < GT; ++h) sc[h * SPLIT + warp * kPage + key] = valid ? s[kk][h] * scale : -INFINITY;
         }
@@ -238,7 +247,7 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ kv, float
 template <typename T>
 __global__ void attn_decode_fast_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               const int* __restrict__ kv_len_arr, T* __restrict__ out, int n_heads,
-                                              int max_splits) {
+                                              int max_splits, int mask, int mask_size, const float* __restrict__ sink) {
     constexpr int SPLIT = Shape<T>::SPLIT;
     pdl_trigger();
     pdl_wait();
@@ -247,14 +256,16 @@ __global__ void attn_decode_fast_merge_kernel(const float* __restrict__ part_o, 
     const int head = blockIdx.x, b = blockIdx.y;
     const int n_splits = min((kv_len_arr[b] + SPLIT - 1) / SPLIT, max_splits);   // (a longer length was cut back and reported)
     const int64_t row0 = ((int64_t)b * n_heads + head) * max_splits;
-    float m = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(row0 + s) * 2]);
-    float denom = 0.f;
-    for (int s = 0; s < n_splits; ++s) denom += expf(part_ml[(row0 + s) * 2] - m) * part_ml[(row0 + s) * 2 + 1];
-    const float inv = n_splits > 0 ? 1.0f / denom : 0.f;
+    // (splits before the first visible key wrote nothing; a sink is a score without a value)
+    const int s_first = kv_len_arr[b] > 0 ? min(first_visible_key(kv_len_arr[b] - 1, mask, mask_size) / SPLIT, n_splits) : 0;
+    float m = sink ? sink[head] : -INFINITY;
+    for (int s = s_first; s < n_splits; ++s) m = fmaxf(m, part_ml[(row0 + s) * 2]);
+    float denom = sink ? expf(sink[head] - m) : 0.f;
+    for (int s = s_first; s < n_splits; ++s) denom += expf(part_ml[(row0 + s) * 2] - m) * part_ml[(row0 + s) * 2 + 1];
+    const float inv = n_splits > s_first ? 1.0f / denom : 0.f;
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
         float v = 0.f;
-        for (int s = 0; s < n_splits; ++s) v = fmaf(expf(part_ml[(row0 + s) * 2] - m), part_o[(row0 + s) * HD + d], v);
+        for (int s = s_first; s < n_splits; ++s) v = fmaf(expf(part_ml[(row0 + s) * 2] - m), part_o[(row0 + s) * HD + d], v);
         st(out + ((int64_t)b * n_heads + head) * HD + d, v * inv);
     }
 }
@@ -262,8 +273,9 @@ __global__ void attn_decode_fast_merge_kernel(const float* __restrict__ part_o, 
 template <typename T>
 int run(const void* q, const void* kv, void* out, float* scratch, int64_t scratch_floats, const int* kv_len, int n_seqs,
         int max_kv_len, const int* page_table, int table_width, int n_heads, int n_kv, float scale, int* status,
-        cudaStream_t s) {
+        cudaStream_t s, int mask = 0, int mask_size = 0, const float* sink = nullptr) {
     using S = Shape<T>;
+    WICK_REQUIRE(mask == 0 || ((mask == 1 || mask == 2) && mask_size > 0), "attention decode: mask %d of size %d", mask, mask_size);
     WICK_REQUIRE(n_heads > 0 && n_kv > 0 && n_heads % n_kv == 0, "attention: %d heads over %d kv heads", n_heads, n_kv);
     WICK_REQUIRE(n_kv <= 65535 && n_seqs <= 65535, "attention: grid limit");
     if (n_seqs == 0) return 0;
@@ -278,10 +290,11 @@ int run(const void* q, const void* kv, void* out, float* scratch, int64_t scratc
         raised = true;
     }
     WICK_CUDA(launch(attn_decode_fast_kernel<T>, dim3(max_splits, n_kv, n_seqs), dim3(S::THREADS), S::SMEM, s, (const T*)q,
-                     (const T*)kv, scratch, ml, kv_len, page_table, table_width, n_heads, n_kv, max_splits, scale, status));
+                     (const T*)kv, scratch, ml, kv_len, page_table, table_width, n_heads, n_kv, max_splits, scale, status, mask,
+                     mask_size));
     if (int e = check_launch("attn_decode")) return e;
     WICK_CUDA(launch(attn_decode_fast_merge_kernel<T>, dim3(n_heads, n_seqs), dim3(HD >= 128 ? 128 : 64), 0, s,
-                     (const float*)scratch, (const float*)ml, kv_len, (T*)out, n_heads, max_splits));
+                     (const float*)scratch, (const float*)ml, kv_len, (T*)out, n_heads, max_splits, mask, mask_size, sink));
     return check_launch("attn_decode_merge");
 }
 
@@ -293,6 +306,23 @@ typedef __nv_bfloat16 bf16;
 
 // Positions per split of the fast decode kernels (the scratch holds, per
 // sequence and head, ceil(max_kv_len / split) partial results of HD + 2 floats).
+// The arguments of wick_attn_decode_bf16 / _f32 below, then the mask (0, or 1 / 2 with its size) and the sinks
+// (float32 [n_heads] or null).
+WICK_API int wick_attn_decode_masked_bf16(const void* q, const void* kv, void* out, float* scratch, long long scratch_floats,
+                                          const int* kv_len, int n_seqs, int max_kv_len, const int* page_table,
+                                          int table_width, int n_heads, int n_kv, float scale, int* status, int mask,
+                                          int mask_size, const float* sink, void* s) {
+    return fastdecode::run<bf16>(q, kv, out, scratch, scratch_floats, kv_len, n_seqs, max_kv_len, page_table, table_width,
+                                 n_heads, n_kv, scale, status, (cudaStream_t)s, mask, mask_size, sink);
+}
+WICK_API int wick_attn_decode_masked_f32(const void* q, const void* kv, void* out, float* scratch, long long scratch_floats,
+                                         const int* kv_len, int n_seqs, int max_kv_len, const int* page_table,
+                                         int table_width, int n_heads, int n_kv, float scale, int* status, int mask,
+                                         int mask_size, const float* sink, void* s) {
+    return fastdecode::run<float>(q, kv, out, scratch, scratch_floats, kv_len, n_seqs, max_kv_len, page_table, table_width,
+                                  n_heads, n_kv, scale, status, (cudaStream_t)s, mask, mask_size, sink);
+}
+
 WICK_API int wick_attn_decode_split_bf16() { return fastdecode::Shape<bf16>::SPLIT; }
 WICK_API int wick_attn_decode_split_f32() { return fastdecode::Shape<float>::SPLIT; }
 

@@ -636,13 +636,16 @@ def qkv_finish(parts: torch.Tensor, n_heads: int, n_kv: int, d: int, e: int, *, 
 
 
 def attention_masked_kind(d: int, v_dim: int, dtype: torch.dtype, is_decode: bool, plain: bool = False) -> str:
-    """Which kernel :func:`attention_masked` runs: ``mma`` (tensor cores through mma.sync: a
-    prompt's tokens in bfloat16 with keys and values of one size, a multiple of 16 up to 128)
-    or ``warp`` (CUDA cores, a warp per token and head: everything else, and the twin that the
-    former is checked against)."""
-    if plain or PLAIN_KERNELS or is_decode or dtype != torch.bfloat16 or d != v_dim or d % 16 != 0 or d > 128:
+    """Which kernel :func:`attention_masked` runs.  With keys and values of one size that is a
+    multiple of 16: ``bulk`` for a decode step (one token per sequence: CUDA cores from bulk-copied
+    page tiles, the positions split over blocks, both dtypes) and ``mma`` for a prompt's tokens in
+    bfloat16 up to size 128 (tensor cores through mma.sync).  Everything else, and the twin that
+    the former are checked against: ``warp`` (CUDA cores straight from the cache)."""
+    if plain or PLAIN_KERNELS or d != v_dim or d % 16 != 0 or d > 256:
         return "warp"
-    return "mma"
+    if is_decode:
+        return "bulk"
+    return "mma" if dtype == torch.bfloat16 and d <= 128 else "warp"
 
 
 def attention_masked(q: torch.Tensor, kv: torch.Tensor, batch, scale: float, *, n_kv: int, v_dim: int,
@@ -663,6 +666,17 @@ def attention_masked(q: torch.Tensor, kv: torch.Tensor, batch, scale: float, *, 
         _cuda("sink", sink, torch.float32, (n_heads,))
     out = torch.empty((n, n_heads, v_dim), dtype=q.dtype, device=q.device)
     kind = kind or attention_masked_kind(d, v_dim, q.dtype, batch.is_decode)
+    if kind == "bulk":
+        _need(d == v_dim and batch.is_decode, "the bulk-copy kernel takes one token per sequence and one head size")
+        mk = batch.kv_bound
+        need = attention_decode_scratch_floats(batch.n_seqs, n_heads, d, mk, q.dtype)
+        ws = getattr(batch, "workspace", None)
+        scratch = ws.get("attention_decode", need, torch.float32) if ws is not None else \
+            torch.empty(need, dtype=torch.float32, device=q.device)
+        _attn(d).call(f"wick_attn_decode_masked_{_dt(q)}", "pppplpiipiiifpiipp", _p(q), _p(kv), _p(out), _p(scratch),
+                      scratch.numel(), _p(batch.kv_len), n, mk, _p(batch.page_table), batch.table_width, n_heads, n_kv,
+                      float(scale), _p(status_tensor(q.device)), MASKS[mask], int(mask_size), _p(sink), _stream(), kernels=2)
+        return out
     if kind == "mma":
         _need(q.dtype == torch.bfloat16 and d == v_dim, "the tensor-core kernel takes bfloat16 and one head size")
         _attn(d).call("wick_attn_prompt_mma_masked_bf16", "pppipippiiifiipp", _p(q), _p(kv), _p(out), attention_tiles(batch),
