@@ -61,7 +61,9 @@ def build_spec(cfg: NibotarConfig) -> ModelSpec:
         final_norm=norm(), final_norm_prefix="final.norm",
         head=PartSpec("linear", {"vocab": cfg.vocab_size, "width": cfg.width, "tied": False, "tensor": "",
                                  "soft_cap": cfg.logit_softcap}),
-        head_prefix="head")
+        head_prefix="head",
+        # (a checkpoint may carry a blend factor for a layer that blends nothing)
+        ignore_tensors=("l*.mix.vmix",))
     spec.validate()
     return spec
 
