@@ -27,8 +27,8 @@ __device__ __forceinline__ int first_visible(int p, int mask, int size) {
 
 // ---------------------------------------------------------------------------
 // One block per token.  The row [q | k | v] (H d + G d + G e numbers) is summed into shared
-// memory; then, in this order: biases, the norms, the rotation (angles from the step's tables), the value
-// blend, and the stores.
+// memory with the biases; the norms' factors follow (all warps); then one pass applies the norm, turns the pairs
+// (angles from the step's tables) and stores q and k, and another blends and stores the values.
 //   v_mode 0: values as projected; 1: also kept in v_keep [n, G e] (float32) for later layers;
 //   2: v <- (1 - lambda) v + lambda v_keep.
 //   pairing 0: (2i, 2i + 1) rotate together; 1: (i, i + rot_dims / 2).
@@ -105,25 +105,10 @@ qkv_finish_kernel(const float* __restrict__ parts, int splits, int64_t split_str
             span_scale[seg] = 1.0f / sqrtf(ss / (float)(seg < nq ? q_span : k_span) + eps);
         }
         __syncthreads();
-        for (int j = tid; j < (q_w ? Wq : 0); j += blockDim.x) row[j] = (row[j] * span_scale[j / q_span]) * q_w[j % q_span];
-        for (int j = tid; j < (k_w ? Wk : 0); j += blockDim.x) row[Wq + j] = (row[Wq + j] * span_scale[nq + j / k_span]) * k_w[j % k_span];
-        __syncthreads();
     }
+    // One pass over the pairs of every q and k head: the norm's factor and weight, the rotation (pairs of the first
+    // rot_dims elements; the others pass), and the store.  Nothing goes back to shared memory.
     const int pos = positions[t];
-    if (cos_t && rot_dims > 0) {
-        const int half = rot_dims >> 1;
-        for (int idx = tid; idx < (H + G) * half; idx += blockDim.x) {
-            const int h = idx / half, i = idx - h * half;
-            float* p = row + h * d;                       // (the k heads follow the q heads at the same stride)
-            const int j0 = pairing == 0 ? 2 * i : i, j1 = pairing == 0 ? 2 * i + 1 : i + half;
-            const float cs = cos_t[(int64_t)t * half + i], sn = sin_t[(int64_t)t * half + i];
-            const float u = p[j0], v = p[j1];
-            p[j0] = u * cs - v * sn;
-            p[j1] = v * cs + u * sn;
-        }
-    }
-    __syncthreads();
-    for (int j = tid; j < Wq; j += blockDim.x) st(q_out + (int64_t)t * Wq + j, row[j]);
     const float lam = v_mode == 2 ? *lambda : 0.f;
     T* page = nullptr;
     if (write_kv) {
@@ -131,9 +116,44 @@ qkv_finish_kernel(const float* __restrict__ parts, int splits, int64_t split_str
         page = kv + (int64_t)pg * G * kPage * (d + e);
     }
     const int r = pos % kPage;
-    for (int j = tid; j < Wk && write_kv; j += blockDim.x) {
-        const int g = j / d, x = j - g * d;
-        st(page + ((int64_t)g * kPage + r) * d + x, row[Wq + j]);
+    const int half = cos_t ? rot_dims >> 1 : 0, rot = 2 * half;
+    const int pairs = half + (d - rot + 1) / 2;            // per head: the turning pairs, then neighbours of the rest
+    for (int idx = tid; idx < (H + G) * pairs; idx += blockDim.x) {
+        const int h = idx / pairs, i = idx - h * pairs;
+        int j0, j1;
+        if (i < half) {
+            j0 = pairing == 0 ? 2 * i : i;
+            j1 = pairing == 0 ? 2 * i + 1 : i + half;
+        } else {
+            j0 = rot + 2 * (i - half);
+            j1 = j0 + 1;                                    // (beyond the head when its size is odd)
+        }
+        const bool is_q = h < H, two = j1 < d;
+        const int base = h * d;                             // (the k heads follow the q heads at the same stride)
+        float u = row[base + j0], v = two ? row[base + j1] : 0.f;
+        const float* w = is_q ? q_w : k_w;
+        if (w) {
+            const int span = is_q ? q_span : k_span;
+            const int o0 = (is_q ? base : base - Wq) + j0, o1 = (is_q ? base : base - Wq) + j1;   // index inside the projection
+            const float sc0 = span_scale[(is_q ? 0 : nq) + o0 / span];
+            u = (u * sc0) * w[o0 % span];
+            if (two) v = (v * span_scale[(is_q ? 0 : nq) + o1 / span]) * w[o1 % span];
+        }
+        if (i < half) {
+            const float cs = cos_t[(int64_t)t * half + i], sn = sin_t[(int64_t)t * half + i];
+            const float ru = u * cs - v * sn, rv = v * cs + u * sn;
+            u = ru;
+            v = rv;
+        }
+        if (is_q) {
+            T* o = q_out + (int64_t)t * Wq + base;
+            st(o + j0, u);
+            if (two) st(o + j1, v);
+        } else if (write_kv) {
+            T* o = page + ((int64_t)(h - H) * kPage + r) * d;
+            st(o + j0, u);
+            if (two) st(o + j1, v);
+        }
     }
     for (int j = tid; j < Wv; j += blockDim.x) {
         float v = row[Wq + Wk + j];
