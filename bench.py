@@ -235,7 +235,7 @@ DESIGN_SIZES = {
 
 def design_configs(z):
     mixer = dict(heads=z["heads"], kv_heads=z["kv"], dim=z["dim"], vdim=z["dim"], scale=z["dim"] ** -0.5, v_mix=True,
-                 mask={"size": z["mask"]}, rot={"dims": z["dim"], "base": 500000.0})
+                 mask={"size": z["mask"]}, rot={"dims": z["dim"], "base": 1000000.0})
     moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]},
            "shared": {"ff": z["shared_ff"]}}
     layers = [dict(type="attention", mixer=mixer, mlp={"kind": "dense", "ff": z["dense_ff"]} if i == 0 else moe)

@@ -115,9 +115,9 @@ def test_norm_after_the_sum():
         x = torch.randn(rows, width, generator=g)
         d = torch.randn(3, rows, width, generator=g)
         w = 0.1 * torch.randn(width, generator=g)
-        ref = P.norm_one_plus(2.5 * x.double() + d.double().sum(0), w.double(), 1e-5)
+        ref = P.norm_one_plus(1.3 * x.double() + d.double().sum(0), w.double(), 1e-5)
         xd = x.to(DEV)
-        out = ops.scaled_add_rmsnorm(xd, d.to(DEV), 2.5, (1.0 + w).to(DEV), 1e-5, torch.bfloat16)
+        out = ops.scaled_add_rmsnorm(xd, d.to(DEV), 1.3, (1.0 + w).to(DEV), 1e-5, torch.bfloat16)
         close(xd, ref, "float32", f"stream, width {width}")
         assert torch.equal(out.float(), xd.to(torch.bfloat16).float())
         xd = x.to(DEV)
@@ -132,7 +132,7 @@ def test_squared_relu_and_soft_cap():
         ad = a.to(dt)
         close(ops.relu_squared_(ad.to(DEV)), torch.relu(ad.double()) ** 2, "float32" if dt == torch.float32 else "bfloat16")
     z = 40 * torch.randn(3, 77, generator=g)
-    close(ops.soft_cap_(z.to(DEV), 15.0), P.softcap(z.double(), 15.0), "float32")
+    close(ops.soft_cap_(z.to(DEV), 12.0), P.softcap(z.double(), 12.0), "float32")
 
 
 @pytest.mark.parametrize("H,G,d,e,span,rot,pairing", [(4, 2, 16, 24, "projection", 8, "neighbours"), (3, 3, 20, 12, "head", 20, "halves"),
