@@ -111,7 +111,7 @@ def one_seq_batch(n_new, start=0, pages=None):
 
 def test_norm_after_the_sum():
     g = torch.Generator().manual_seed(1)
-    for width, rows in ((48, 9), (100, 9), (257, 9), (100, 600), (2052, 515)):      # few rows: a block per row; many: a warp
+    for width, rows in ((48, 9), (100, 9), (257, 9), (100, 600), (2052, 515)):
         x = torch.randn(rows, width, generator=g)
         d = torch.randn(3, rows, width, generator=g)
         w = 0.1 * torch.randn(width, generator=g)

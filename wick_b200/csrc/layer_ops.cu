@@ -71,66 +71,6 @@ scaled_add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta
     }
 }
 
-// The same for many rows that are a multiple of 4 wide and at most 4096: one warp per row, the row in
-// registers (lane l holds the quads l, l + 32, ...), nothing synchronised but the warp.  The sum of squares
-// is taken in another order than in the block's form: the two differ by rounding.
-__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) { *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d); }
-__device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float c, float d) {
-    uint2 u;
-    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
-    u.x = *reinterpret_cast<uint32_t*>(&lo);
-    u.y = *reinterpret_cast<uint32_t*>(&hi);
-    *reinterpret_cast<uint2*>(p) = u;
-}
-
-template <typename TOut>
-__global__ void __launch_bounds__(128)
-scaled_add_rmsnorm_rows_kernel(float* __restrict__ x, const float* __restrict__ delta, int splits, int64_t split_stride,
-                               float alpha, const float* __restrict__ w, float eps, TOut* __restrict__ out, int n, int width) {
-    pdl_trigger();
-    pdl_wait();
-    x = fresh(x);
-    delta = fresh(delta);
-    constexpr int QMAX = 4096 / 4 / 32;
-    const int lane = threadIdx.x & 31;
-    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (r >= n) return;
-    float* xr = x + (int64_t)r * width;
-    float4 v[QMAX];
-#pragma unroll
-    for (int m = 0; m < QMAX; ++m) {
-        const int j = (lane + 32 * m) * 4;
-        v[m] = j < width ? *reinterpret_cast<const float4*>(xr + j) : make_float4(0.f, 0.f, 0.f, 0.f);
-        v[m].x *= alpha; v[m].y *= alpha; v[m].z *= alpha; v[m].w *= alpha;
-    }
-    for (int s = 0; s < splits; ++s) {
-#pragma unroll
-        for (int m = 0; m < QMAX; ++m) {
-            const int j = (lane + 32 * m) * 4;
-            if (j < width) {
-                const float4 d = *reinterpret_cast<const float4*>(delta + s * split_stride + (int64_t)r * width + j);
-                v[m].x += d.x; v[m].y += d.y; v[m].z += d.z; v[m].w += d.w;
-            }
-        }
-    }
-    float ss = 0.f;
-#pragma unroll
-    for (int m = 0; m < QMAX; ++m) {
-        ss = fmaf(v[m].x, v[m].x, ss); ss = fmaf(v[m].y, v[m].y, ss); ss = fmaf(v[m].z, v[m].z, ss); ss = fmaf(v[m].w, v[m].w, ss);
-    }
-    const float scale = 1.0f / sqrtf(warp_sum(ss) / (float)width + eps);
-#pragma unroll
-    for (int m = 0; m < QMAX; ++m) {
-        const int j = (lane + 32 * m) * 4;
-        if (j < width) {
-            const float4 g = *reinterpret_cast<const float4*>(w + j);
-            const float a = (v[m].x * scale) * g.x, b = (v[m].y * scale) * g.y, c = (v[m].z * scale) * g.z, d = (v[m].w * scale) * g.w;
-            store4(xr + j, a, b, c, d);
-            if (out) store4(out + (int64_t)r * width + j, a, b, c, d);
-        }
-    }
-}
-
 // Eight elements a thread where the array allows 16-byte accesses (vec), else one.
 template <typename T>
 __global__ void relu_squared_kernel(T* __restrict__ a, int64_t n, int vec) {
@@ -180,12 +120,6 @@ int scaled_add_rmsnorm(float* x, const float* delta, int splits, float alpha, co
                        int width, cudaStream_t s) {
     WICK_REQUIRE(width > 0 && n >= 0 && splits >= 0, "scaled_add_rmsnorm: bad sizes");
     if (n == 0) return 0;
-    if (n >= 512 && width % 4 == 0 && width <= 4096 && (((uintptr_t)x | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)out) & 15) == 0) {
-        // enough rows to give every multiprocessor its warps: a warp per row
-        WICK_CUDA(launch(scaled_add_rmsnorm_rows_kernel<TOut>, dim3(ceil_div(n, 4)), dim3(128), 0, s, x, delta, splits,
-                         (int64_t)n * width, alpha, w, eps, (TOut*)out, n, width));
-        return check_launch("scaled_add_rmsnorm");
-    }
     const size_t smem = ((size_t)((width + 3) & ~3) + 40) * sizeof(float);
     WICK_REQUIRE(smem <= 200 * 1024, "scaled_add_rmsnorm: width %d is beyond one block's shared memory", width);
     static bool raised = false;
