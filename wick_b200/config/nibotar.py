@@ -121,6 +121,22 @@ class NibotarConfig(ModelConfig):
     def max_position(self) -> int:
         return 1 << 30                     # (the design names no limit; positions are 32-bit integers)
 
+    def param_count(self, tied: Optional[bool] = None) -> int:
+        """Number of parameters (every expert counted)."""
+        n = 2 * self.vocab_size * self.width + self.width
+        for L in self.layers:
+            m = L.mixer
+            q, k, v = m.heads * m.dim, m.kv_heads * m.dim, m.kv_heads * m.vdim
+            n += (q + k + v) * (self.width + 1) + q + k + m.heads + 1 + self.width * m.heads * m.vdim + self.width
+            if L.mlp is None:
+                continue
+            n += self.width
+            if L.mlp.kind == "dense":
+                n += 2 * self.width * L.mlp.ff
+            else:
+                n += 3 * self.width * (L.mlp.experts * L.mlp.ff + (L.mlp.shared_ff or 0)) + self.vocab_size * L.mlp.top
+        return n
+
     @classmethod
     def from_json(cls, j: Mapping[str, Any], architecture: str) -> "NibotarConfig":
         raw = j.get("layers")
