@@ -168,12 +168,18 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
 // keys, a row holds 64 consecutive dims in 128 bytes, eight rows make a 1024-byte
 // group, and the next 64 dims lie one panel (the leading offset) further.
 
+// First key that the query at position p sees: mask 0 every earlier key, 1 those of p's own block of `size`
+// positions (blocks counted from position 0), 2 the last `size` positions.
+__device__ __forceinline__ int first_visible_key(int p, int mask, int size) {
+    return mask == 1 ? p / size * size : (mask == 2 ? max(0, p - size + 1) : 0);
+}
+
 __global__ void __launch_bounds__(THREADS, 1)
 attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
                       bf16* __restrict__ out, const int* __restrict__ cu_seqlens, int n_seqs,
                       const int* __restrict__ start_arr,
                       const int* __restrict__ page_table, int table_width, int n_tiles, int n_heads, int n_kv,
-                      float scale, int* status) {
+                      float scale, int* status, int mask, int mask_size, const float* __restrict__ sink) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t q_full, full[NSLOT];
     __shared__ uint64_t s_full[NBUF], p_full[NBUF], pv_done[2], v_free[NBUF], x_bar[4];   // pv_done: even blocks, odd blocks
@@ -192,7 +198,10 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
     const int kv_len = start + q_len;
     const int rows = min(BQ, q_len - q0);
     const int last_key = min(start + q0 + BQ - 1, kv_len - 1);     // the last position any row of the block may see
-    const int n_blk = last_key / BK + 1;
+    // With a mask the first block of keys is the one that holds the first row's first visible key (the first
+    // visible key grows with the position); blocks are counted from there, j = 0 .. n_blk - 1, everywhere below.
+    const int jb0 = first_visible_key(start + q0, mask, mask_size) / BK;
+    const int n_blk = last_key / BK + 1 - jb0;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -245,7 +254,7 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
                 }
                 mbar_expect_tx(&full[slot], TILE_BYTES);
                 for (int w = 0; w < 2; ++w) {
-                    const int idx = 2 * j + w;
+                    const int idx = 2 * (j + jb0) + w;
                     const int page = idx < table_width ? page_table[(int64_t)b * table_width + idx] : 0;
                     for (int pn = 0; pn < PANELS; ++pn)
                         tma_load_2d(&kv_map, &full[slot], kv_s + slot * TILE_BYTES + pn * PANEL_BYTES + w * (kPage * 128), pn * 64,
@@ -304,13 +313,16 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
         const int c_lo = half * HALF_K;
         const int q_pos = start + q0 + r;
         const int limit = min(q_pos, kv_len - 1);                   // last visible key position
+        const int vis = first_visible_key(limit, mask, mask_size);  // first visible key position
         const float sl2 = scale * 1.4426950408889634f;
+        const float sink2 = sink ? sink[head] * 1.4426950408889634f : -INFINITY;   // a score without a value
         const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
         constexpr int OW = HD / 2;                                  // columns of O this thread rescales and stores
         const uint32_t o_addr = lane_base + COL_O + half * OW;
         // m: the maximum (in units of log2 e) that O and l are scaled by.  It follows
         // the true running maximum lazily; l: this thread's part of the row's sum.
-        float m = -INFINITY, l = 0.f;
+        // (a sink: the scaling maximum starts there, and its share joins the row's sum at the end)
+        float m = sink2, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_blk; ++j) {
             const int buf = j % NBUF, xb = j & 1, v_item = 2 * j + 1, v_slot = v_item % NSLOT;
@@ -318,15 +330,15 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
             ok = __all_sync(0xffffffffu, mbar_wait(&s_full[buf], (j / NBUF) & 1, &abort_flag, status, 7));
             if (!ok) break;
             tc_fence_after();
-            const int key0 = j * BK + c_lo;
+            const int key0 = (j + jb0) * BK + c_lo;
             float s[HALF_K];
             tc_ld32_nowait(s_addr + c_lo, reinterpret_cast<uint32_t*>(s));
             tc_ld32_nowait(s_addr + c_lo + 32, reinterpret_cast<uint32_t*>(s + 32));
             tc_ld_wait();
-            if (key0 + HALF_K - 1 > limit) {
+            if (key0 + HALF_K - 1 > limit || key0 < vis) {
 #pragma unroll
                 for (int i = 0; i < HALF_K; ++i)
-                    if (key0 + i > limit) s[i] = -INFINITY;
+                    if (key0 + i > limit || key0 + i < vis) s[i] = -INFINITY;
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -391,7 +403,7 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
             tc_st_wait();
             l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             // value rows that hold no token yet are made zero before they are multiplied
-            const int valid = kv_len - j * BK;
+            const int valid = kv_len - (j + jb0) * BK;
             if (valid < BK) {
                 ok = __all_sync(0xffffffffu, mbar_wait(&full[v_slot], (v_item / NSLOT) & 1, &abort_flag, status, 7));
                 if (!ok) break;
@@ -421,7 +433,7 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
         }
         if (ok) {
             // every lane takes part in the loads from tensor memory; only rows that exist are stored
-            const float l_row = l_x[r] + l_x[BQ + r];
+            const float l_row = l_x[r] + l_x[BQ + r] + (sink ? ex2(sink2 - m) : 0.f);   // (both halves scale by the same m)
             const bool store = r < rows && l_row > 0.f;
             const float inv = store ? 1.0f / l_row : 0.f;
             bf16* dst = out + ((int64_t)(tok0 + q0 + r) * n_heads + head) * HD + half * OW;
@@ -470,11 +482,13 @@ WICK_API int wick_attn_prompt_tc_supported() { return prompttc::SUPPORTED ? 1 : 
 // [kv_pages, 2, n_kv, 64, HD] (it already holds the new tokens' keys and values);
 // n_tiles: the step's 64-row work items (one per 64 new tokens of a sequence, numbered
 // sequence by sequence); status: device int (code 7 if a block gave up waiting).
-WICK_API int wick_attn_prompt_tc_bf16(const void* q, long long n_tokens, const void* kv, long long kv_pages, void* out,
-                                      int n_tiles, const int* cu_seqlens, int n_seqs,
-                                      const int* start, const int* page_table, int table_width, int n_heads, int n_kv,
-                                      float scale, int* status, void* s) {
+// ... then the mask (0, or 1 / 2 with its size) and the sinks (float32 [n_heads] or null).
+WICK_API int wick_attn_prompt_tc_masked_bf16(const void* q, long long n_tokens, const void* kv, long long kv_pages, void* out,
+                                             int n_tiles, const int* cu_seqlens, int n_seqs,
+                                             const int* start, const int* page_table, int table_width, int n_heads, int n_kv,
+                                             float scale, int* status, int mask, int mask_size, const float* sink, void* s) {
     using namespace prompttc;
+    WICK_REQUIRE(mask == 0 || ((mask == 1 || mask == 2) && mask_size > 0), "attention: mask %d of size %d", mask, mask_size);
     WICK_REQUIRE(SUPPORTED, "attention (tcgen05): head_dim %d is not 64 or 128", (int)WICK_HD);
     WICK_REQUIRE(n_heads > 0 && n_kv > 0 && n_heads % n_kv == 0, "attention: %d heads over %d kv heads", n_heads, n_kv);
     WICK_REQUIRE(n_heads <= 65535, "attention: %d heads is beyond the grid limit", n_heads);
@@ -489,6 +503,14 @@ WICK_API int wick_attn_prompt_tc_bf16(const void* q, long long n_tokens, const v
     }
     WICK_CUDA(launch(attn_prompt_tc_kernel, dim3(n_tiles, n_heads), dim3(THREADS), (size_t)SMEM_BYTES, (cudaStream_t)s, q_map,
                      kv_map, (bf16*)out, cu_seqlens, n_seqs, start, page_table, table_width, n_tiles, n_heads,
-                     n_kv, scale, status));
+                     n_kv, scale, status, mask, mask_size, sink));
     return check_launch("attn_prompt_tc");
+}
+
+WICK_API int wick_attn_prompt_tc_bf16(const void* q, long long n_tokens, const void* kv, long long kv_pages, void* out,
+                                      int n_tiles, const int* cu_seqlens, int n_seqs,
+                                      const int* start, const int* page_table, int table_width, int n_heads, int n_kv,
+                                      float scale, int* status, void* s) {
+    return wick_attn_prompt_tc_masked_bf16(q, n_tokens, kv, kv_pages, out, n_tiles, cu_seqlens, n_seqs, start, page_table,
+                                           table_width, n_heads, n_kv, scale, status, 0, 0, nullptr, s);
 }

@@ -638,14 +638,16 @@ def qkv_finish(parts: torch.Tensor, n_heads: int, n_kv: int, d: int, e: int, *, 
 def attention_masked_kind(d: int, v_dim: int, dtype: torch.dtype, is_decode: bool, plain: bool = False) -> str:
     """Which kernel :func:`attention_masked` runs.  With keys and values of one size that is a
     multiple of 16: ``bulk`` for a decode step (one token per sequence: CUDA cores from bulk-copied
-    page tiles, the positions split over blocks, both dtypes) and ``mma`` for a prompt's tokens in
-    bfloat16 up to size 128 (tensor cores through mma.sync).  Everything else, and the twin that
+    page tiles, the positions split over blocks, both dtypes); for a prompt's tokens in bfloat16
+    ``tc`` (tcgen05, sizes 64 and 128) or ``mma`` (mma.sync, other sizes up to 128).  Everything else, and the twin that
     the former are checked against: ``warp`` (CUDA cores straight from the cache)."""
     if plain or PLAIN_KERNELS or d != v_dim or d % 16 != 0 or d > 256:
         return "warp"
     if is_decode:
         return "bulk"
-    return "mma" if dtype == torch.bfloat16 and d <= 128 else "warp"
+    if dtype != torch.bfloat16 or d > 128:
+        return "warp"
+    return "tc" if d in (64, 128) else "mma"
 
 
 def attention_masked(q: torch.Tensor, kv: torch.Tensor, batch, scale: float, *, n_kv: int, v_dim: int,
@@ -676,6 +678,13 @@ def attention_masked(q: torch.Tensor, kv: torch.Tensor, batch, scale: float, *, 
         _attn(d).call(f"wick_attn_decode_masked_{_dt(q)}", "pppplpiipiiifpiipp", _p(q), _p(kv), _p(out), _p(scratch),
                       scratch.numel(), _p(batch.kv_len), n, mk, _p(batch.page_table), batch.table_width, n_heads, n_kv,
                       float(scale), _p(status_tensor(q.device)), MASKS[mask], int(mask_size), _p(sink), _stream(), kernels=2)
+        return out
+    if kind == "tc":
+        _need(q.dtype == torch.bfloat16 and d == v_dim and d in (64, 128), "the tcgen05 kernel takes bfloat16 heads of 64 or 128")
+        _attn(d).call("wick_attn_prompt_tc_masked_bf16", "plplpipippiiifpiipp", _p(q), n, _p(kv), kv.shape[0], _p(out),
+                      attention_tiles(batch), _p(batch.cu_seqlens), batch.n_seqs, _p(batch.start), _p(batch.page_table),
+                      batch.table_width, n_heads, n_kv, float(scale), _p(status_tensor(q.device)), MASKS[mask], int(mask_size),
+                      _p(sink), _stream())
         return out
     if kind == "mma":
         _need(q.dtype == torch.bfloat16 and d == v_dim, "the tensor-core kernel takes bfloat16 and one head size")
