@@ -1,7 +1,7 @@
 """wick_b200: a small model library with generation for one NVIDIA B200.
 
 Everything between a request's token ids and its next token for the Qwen3 dense
-decoder and the Nibotar decoder: typed configuration and architecture registry, safetensors weights (or
+decoder, the Nibotar decoder and the Tuguvik decoder: typed configuration and architecture registry, safetensors weights (or
 seeded random ones), layers assembled from registered parts, a paged cache with
 a slot per sequence, one step function for batches of unequal sequences, a
 generation loop, sampling, and hand-written CUDA kernels for sm_100a.
@@ -15,8 +15,10 @@ from .config.base import (ConfigError, ModelConfig, architecture_names, config_f
                           load_config, register_architecture, Architecture)
 from .config.nibotar import NibotarConfig
 from .config.qwen3 import Qwen3Config
+from .config.tuguvik import TuguvikConfig
 from .models import qwen3 as _qwen3  # registers the architecture  # noqa: F401
 from .models import nibotar as _nibotar  # noqa: F401
+from .models import tuguvik as _tuguvik  # noqa: F401
 from .models.model import Model
 from .models.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from .sampling.sampler import Rng, Sampler, SamplerConfig
@@ -37,6 +39,6 @@ def __getattr__(name):
 
 __all__ = ["Architecture", "ConfigError", "Engine", "GenOptions", "GenResult", "LayerSpec", "Model", "ModelConfig",
            "ModelSpec", "NibotarConfig", "PartSpec", "Qwen3Config", "Rng", "SafeTensorsDir", "SafeTensorsError", "Sampler",
-           "SamplerConfig", "ScheduleEntry", "WeightError", "architecture_names", "config_from_json", "generate",
+           "SamplerConfig", "ScheduleEntry", "TuguvikConfig", "WeightError", "architecture_names", "config_from_json", "generate",
            "get_architecture", "load_config", "load_weights", "register_architecture", "write_random_model",
            "write_safetensors"]

@@ -11,7 +11,9 @@
 * Schedule entries (layers as they run) with equal needs form a **group** with
   storage of its own, of the class registered for the need's kind
   (:func:`register_storage`): ``paged_kv`` groups [entries, pages, 2, kv_heads,
-  64, head_dim]; ``state`` groups [entries, slots, *shape], a record of fixed
+  64, head_dim]; ``paged_rows`` groups [entries, pages, 64, *shape], one row of
+  fixed shape per position (a latent that keys and values are made from);
+  ``state`` groups [entries, slots, *shape], a record of fixed
   size per sequence that is zeroed when the sequence opens.  All paged groups
   share the page ids (page p of a sequence is page p in each group).  Another
   kind of storage (a ring of the last positions, say) is another registered
@@ -125,6 +127,27 @@ class PagedKV(Storage):
         return cached_tokens * self.bytes_per_token()
 
 
+class PagedRows(Storage):
+    """One row of the need's ``shape`` per position: [entries, pages, 64, *shape].  A mixer
+    sees its entry's part as ``rows``."""
+    kind = "paged_rows"
+
+    def shape(self):
+        return (self.n_entries, self.n_pages, PAGE) + tuple(self.need.shape)
+
+    def view(self, idx, batch):
+        return CacheView(rows=self.tensor[idx])
+
+    def bytes_per_token(self) -> int:
+        n = self.n_entries * self.element_size()
+        for d in self.need.shape:
+            n *= d
+        return n
+
+    def read_bytes(self, cached_tokens, n_seqs):
+        return cached_tokens * self.bytes_per_token()
+
+
 class StateRecords(Storage):
     """A record of fixed shape per sequence: [entries, slots, *shape], zero when a sequence starts."""
     kind = "state"
@@ -155,6 +178,7 @@ def register_storage(kind: str, cls: type) -> type:
 
 
 register_storage("paged_kv", PagedKV)
+register_storage("paged_rows", PagedRows)
 register_storage("state", StateRecords)
 
 
@@ -212,7 +236,7 @@ class Cache:
     # ---- sizes -------------------------------------------------------------
     def bytes_per_token(self) -> int:
         """Bytes of keys and values that one cached position takes in all paged groups."""
-        return sum(g.store.bytes_per_token() for g in self.groups if isinstance(g.store, PagedKV))
+        return sum(g.store.bytes_per_token() for g in self.groups if isinstance(g.store, (PagedKV, PagedRows)))
 
     def read_bytes(self, cached_tokens: int, n_seqs: int) -> int:
         """Bytes one decode step reads from the cache: every group's share for ``n_seqs``

@@ -32,6 +32,8 @@ __device__ __forceinline__ int first_visible(int p, int mask, int size) {
 //   v_mode 0: values as projected; 1: also kept in v_keep [n, G e] (float32) for later layers;
 //   2: v <- (1 - lambda) v + lambda v_keep.
 //   pairing 0: (2i, 2i + 1) rotate together; 1: (i, i + rot_dims / 2).
+//   maps: a q or k head of d numbers is `maps` vectors of d / maps, side by side, each of which is
+//   turned on its own (the first rot_dims elements of each); 1: the head is one vector.
 constexpr int MAX_SPANS = 512;                  // spans of the two norms together (a span per head at most)
 
 template <typename T>
@@ -39,7 +41,7 @@ __global__ void __launch_bounds__(256)
 qkv_finish_kernel(const float* __restrict__ parts, int splits, int64_t split_stride, const float* __restrict__ bias,
                   int H, int G, int d, int e, const float* __restrict__ q_w, int q_span, const float* __restrict__ k_w,
                   int k_span, float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_dims,
-                  int pairing, float* __restrict__ v_keep, int v_mode, const float* __restrict__ lambda, T* __restrict__ q_out,
+                  int pairing, int maps, float* __restrict__ v_keep, int v_mode, const float* __restrict__ lambda, T* __restrict__ q_out,
                   T* __restrict__ kv, const int* __restrict__ page_table, int table_width,
                   const int* __restrict__ seq_of_token, const int* __restrict__ positions, int write_kv) {
     extern __shared__ float row[];
@@ -117,9 +119,10 @@ qkv_finish_kernel(const float* __restrict__ parts, int splits, int64_t split_str
     }
     const int r = pos % kPage;
     const int half = cos_t ? rot_dims >> 1 : 0, rot = 2 * half;
-    const int pairs = half + (d - rot + 1) / 2;            // per head: the turning pairs, then neighbours of the rest
-    for (int idx = tid; idx < (H + G) * pairs; idx += blockDim.x) {
-        const int h = idx / pairs, i = idx - h * pairs;
+    const int dm = d / maps;                               // a vector that turns on its own (the whole head, or one of its maps)
+    const int pairs = half + (dm - rot + 1) / 2;           // per vector: the turning pairs, then neighbours of the rest
+    for (int idx = tid; idx < (H + G) * maps * pairs; idx += blockDim.x) {
+        const int h = idx / pairs, i = idx - h * pairs;     // h counts the vectors: q's, then k's
         int j0, j1;
         if (i < half) {
             j0 = pairing == 0 ? 2 * i : i;
@@ -128,8 +131,8 @@ qkv_finish_kernel(const float* __restrict__ parts, int splits, int64_t split_str
             j0 = rot + 2 * (i - half);
             j1 = j0 + 1;                                    // (beyond the head when its size is odd)
         }
-        const bool is_q = h < H, two = j1 < d;
-        const int base = h * d;                             // (the k heads follow the q heads at the same stride)
+        const bool is_q = h < H * maps, two = j1 < dm;
+        const int base = h * dm;                            // (the k vectors follow the q vectors at the same stride)
         float u = row[base + j0], v = two ? row[base + j1] : 0.f;
         const float* w = is_q ? q_w : k_w;
         if (w) {
@@ -150,7 +153,8 @@ qkv_finish_kernel(const float* __restrict__ parts, int splits, int64_t split_str
             st(o + j0, u);
             if (two) st(o + j1, v);
         } else if (write_kv) {
-            T* o = page + ((int64_t)(h - H) * kPage + r) * d;
+            const int kh = (h - H * maps) / maps, km = (h - H * maps) - kh * maps;
+            T* o = page + ((int64_t)kh * kPage + r) * d + km * dm;
             st(o + j0, u);
             if (two) st(o + j1, v);
         }
@@ -492,14 +496,15 @@ attn_masked_group_kernel(const T* __restrict__ q, const T* __restrict__ kv, T* _
 template <typename T>
 int qkv_finish(const float* parts, int splits, int n, const float* bias, int H, int G, int d, int e, const float* q_w,
                int q_span, const float* k_w, int k_span, float eps, const float* cos_t, const float* sin_t, int rot_dims,
-               int pairing, float* v_keep, int v_mode, const float* lambda, void* q_out, void* kv, const int* page_table,
+               int pairing, int maps, float* v_keep, int v_mode, const float* lambda, void* q_out, void* kv, const int* page_table,
                int table_width, const int* seq_of_token, const int* positions, int write_kv, cudaStream_t s) {
     WICK_REQUIRE(H > 0 && G > 0 && H % G == 0 && d > 0 && e > 0, "qkv_finish: bad head counts or sizes");
+    WICK_REQUIRE(maps >= 1 && d % maps == 0, "qkv_finish: a head of %d numbers is not %d vectors", d, maps);
     WICK_REQUIRE(splits >= 1, "qkv_finish: partial sums are needed");
     const int Wq = H * d, Wk = G * d;
     if (q_w) WICK_REQUIRE(q_span > 0 && Wq % q_span == 0, "qkv_finish: a q norm span of %d does not divide %d", q_span, Wq);
     if (k_w) WICK_REQUIRE(k_span > 0 && Wk % k_span == 0, "qkv_finish: a k norm span of %d does not divide %d", k_span, Wk);
-    WICK_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= d, "qkv_finish: %d rotated dims of %d", rot_dims, d);
+    WICK_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= d / maps, "qkv_finish: %d rotated dims of %d", rot_dims, d / maps);
     WICK_REQUIRE((cos_t == nullptr) == (sin_t == nullptr), "qkv_finish: the two angle tables come together");
     WICK_REQUIRE((q_w ? Wq / q_span : 0) + (k_w ? Wk / k_span : 0) <= MAX_SPANS, "qkv_finish: too many norm spans");
     WICK_REQUIRE(v_mode == 0 || v_keep, "qkv_finish: the kept values are missing");
@@ -513,7 +518,7 @@ int qkv_finish(const float* parts, int splits, int n, const float* bias, int H, 
         raised = true;
     }
     WICK_CUDA(launch(qkv_finish_kernel<T>, dim3(n), dim3(256), smem, s, parts, splits, (int64_t)n * (Wq + Wk + G * e), bias, H, G,
-                     d, e, q_w, q_span, k_w, k_span, eps, cos_t, sin_t, rot_dims, pairing, v_keep, v_mode, lambda, (T*)q_out,
+                     d, e, q_w, q_span, k_w, k_span, eps, cos_t, sin_t, rot_dims, pairing, maps, v_keep, v_mode, lambda, (T*)q_out,
                      (T*)kv, page_table, table_width, seq_of_token, positions, write_kv));
     return check_launch("qkv_finish");
 }
@@ -562,11 +567,11 @@ typedef __nv_bfloat16 bf16;
 #define WICK_QKV_FINISH(NAME, T)                                                                                              \
     WICK_API int NAME(const float* parts, int splits, int n, const float* bias, int H, int G, int d, int e, const float* q_w,    \
                       int q_span, const float* k_w, int k_span, float eps, const float* cos_t, const float* sin_t,               \
-                      int rot_dims, int pairing, float* v_keep, int v_mode, const float* lambda, void* q_out, void* kv,          \
+                      int rot_dims, int pairing, int maps, float* v_keep, int v_mode, const float* lambda, void* q_out, void* kv, \
                       const int* page_table, int table_width, const int* seq_of_token, const int* positions, int write_kv,       \
                       void* s) {                                                                                                 \
         return qkv_finish<T>(parts, splits, n, bias, H, G, d, e, q_w, q_span, k_w, k_span, eps, cos_t, sin_t, rot_dims, pairing,  \
-                             v_keep, v_mode, lambda, q_out, kv, page_table, table_width, seq_of_token, positions, write_kv,      \
+                             maps, v_keep, v_mode, lambda, q_out, kv, page_table, table_width, seq_of_token, positions, write_kv,      \
                              (cudaStream_t)s);                                                                                   \
     }
 WICK_QKV_FINISH(wick_qkv_finish_bf16, bf16)

@@ -226,7 +226,7 @@ __global__ void add_delta_kernel(float* __restrict__ x, const float* __restrict_
 
 // ---- rotary tables ---------------------------------------------------------
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
-                                  float* __restrict__ cos_t, float* __restrict__ sin_t, int n, int half) {
+                                  float* __restrict__ cos_t, float* __restrict__ sin_t, int n, int half, float amplitude) {
     pdl_trigger();
     pdl_wait();
     int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -235,8 +235,8 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
     const float angle = (float)positions[t] * inv_freq[i];
     float s, c;
     sincosf(angle, &s, &c);
-    cos_t[idx] = c;
-    sin_t[idx] = s;
+    cos_t[idx] = amplitude == 1.0f ? c : c * amplitude;
+    sin_t[idx] = amplitude == 1.0f ? s : s * amplitude;
 }
 
 // Two neighbouring elements at an even index.
@@ -561,10 +561,10 @@ WICK_API int wick_add_delta(float* x, const float* delta, int splits, int64_t n,
 }
 
 WICK_API int wick_rope_table(const int* positions, const float* inv_freq, float* cos_t, float* sin_t, int n,
-                             int half, void* s) {
+                             int half, float amplitude, void* s) {
     if (n == 0 || half == 0) return 0;
     WICK_CUDA(launch(rope_table_kernel, dim3(ceil_div((int64_t)n * half, 256)), dim3(256), 0, (cudaStream_t)s, positions,
-                     inv_freq, cos_t, sin_t, n, half));
+                     inv_freq, cos_t, sin_t, n, half, amplitude));
     return check_launch("rope_table");
 }
 

@@ -7,6 +7,10 @@
 //                in the activation type for the next matrix product.
 //   relu^2    :  a <- max(a, 0)^2
 //   soft cap  :  z <- c * tanh(z / c)
+//   stream    :  x <- x + f(d_0 + d_1 + ...), f the identity, a factor per element, or
+//                rms(.) * g (times a factor per element), optionally followed by the
+//                norm y = tanh(a x) * w + b or by a copy of x in the activation type
+//   gate rows :  g = gelu_tanh(z) * e, e a slice of the token's row in a table
 #include "common.cuh"
 
 namespace wick {
@@ -115,6 +119,134 @@ __global__ void to_activation_kernel(const float* __restrict__ x, T* __restrict_
     if (i < n) st(out + i, x[i]);
 }
 
+// One block per output row i; source row r = rows ? rows[i] : i.
+//   v = x[r] + f(sum of the partial sums, in index order), where f divides by the root mean square and multiplies
+//   by rms_w (if given), then multiplies by scale (if given);  v goes back to x[r] unless rows are selected (a row
+//   may be named twice, and nobody reads x afterwards then);  out[i] = tanh(alpha v) * w + b if w is given, else v.
+// With rms_w the sums wait in shared memory between the pass that squares them and the pass that uses them;
+// otherwise one pass does everything, four neighbours a thread where the width allows.
+template <typename TOut>
+__global__ void __launch_bounds__(1024)
+stream_update_kernel(float* __restrict__ x, const float* __restrict__ delta, int splits, int64_t split_stride,
+                     const float* __restrict__ scale, const float* __restrict__ rms_w, float rms_eps,
+                     const float* __restrict__ alpha, const float* __restrict__ w, const float* __restrict__ b,
+                     const int* __restrict__ rows, TOut* __restrict__ out, int width) {
+    extern __shared__ float smem[];
+    float* row = smem;
+    float* red = smem + ((width + 3) & ~3);
+    pdl_trigger();
+    const float a = alpha ? *alpha : 0.f;              // (a weight: no kernel writes it)
+    pdl_wait();
+    x = fresh(x);
+    delta = fresh(delta);
+    const int i = blockIdx.x;
+    const int64_t r = rows ? rows[i] : i;
+    float* xr = x + r * width;
+    TOut* o = out ? out + (int64_t)i * width : nullptr;
+    const bool vec = (width & 3) == 0 && (split_stride & 3) == 0;
+    float f = 1.f;
+    if (delta && rms_w) {
+        float ss = 0.f;
+        if (vec) {
+            for (int j = threadIdx.x * 4; j < width; j += blockDim.x * 4) {
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                add_partials4(v, delta, splits, split_stride, r * width + j);
+                *reinterpret_cast<float4*>(row + j) = v;
+                ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+            }
+        } else {
+            for (int j = threadIdx.x; j < width; j += blockDim.x) {
+                float v = 0.f;
+                for (int s = 0; s < splits; ++s) v += delta[s * split_stride + r * width + j];
+                row[j] = v;
+                ss = fmaf(v, v, ss);
+            }
+        }
+        ss = block_sum(ss, red);
+        f = 1.0f / sqrtf(ss / (float)width + rms_eps);
+    }
+    auto finish = [&](int j, float xv, float d) -> float {
+        if (delta) {
+            if (rms_w) d = (d * f) * rms_w[j];
+            if (scale) d *= scale[j];
+            xv += d;
+        }
+        return xv;
+    };
+    if (vec) {
+        for (int j = threadIdx.x * 4; j < width; j += blockDim.x * 4) {
+            const float4 xv = *reinterpret_cast<const float4*>(xr + j);
+            float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (delta) {
+                if (rms_w) d = *reinterpret_cast<const float4*>(row + j);
+                else add_partials4(d, delta, splits, split_stride, r * width + j);
+            }
+            float4 v;
+            v.x = finish(j, xv.x, d.x); v.y = finish(j + 1, xv.y, d.y); v.z = finish(j + 2, xv.z, d.z); v.w = finish(j + 3, xv.w, d.w);
+            if (delta && !rows) *reinterpret_cast<float4*>(xr + j) = v;
+            if (o) {
+                if (w) {
+                    st(o + j, tanhf(a * v.x) * w[j] + b[j]);
+                    st(o + j + 1, tanhf(a * v.y) * w[j + 1] + b[j + 1]);
+                    st(o + j + 2, tanhf(a * v.z) * w[j + 2] + b[j + 2]);
+                    st(o + j + 3, tanhf(a * v.w) * w[j + 3] + b[j + 3]);
+                } else {
+                    st(o + j, v.x); st(o + j + 1, v.y); st(o + j + 2, v.z); st(o + j + 3, v.w);
+                }
+            }
+        }
+    } else {
+        for (int j = threadIdx.x; j < width; j += blockDim.x) {
+            float d = 0.f;
+            if (delta) {
+                if (rms_w) d = row[j];
+                else for (int s = 0; s < splits; ++s) d += delta[s * split_stride + r * width + j];
+            }
+            const float v = finish(j, xr[j], d);
+            if (delta && !rows) xr[j] = v;
+            if (o) st(o + j, w ? tanhf(a * v) * w[j] + b[j] : v);
+        }
+    }
+}
+
+// out[t, j] = gelu_tanh(z[t, j]) * table[tokens[t], offset + j]; gelu_tanh(z) = z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+template <typename T>
+__global__ void gelu_gate_rows_kernel(const float* __restrict__ z, const T* __restrict__ table, const int* __restrict__ tokens,
+                                      T* __restrict__ out, int64_t n, int dim, int64_t row_width, int offset) {
+    pdl_trigger();
+    pdl_wait();
+    z = fresh(z);
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n * dim) return;
+    const int64_t t = i / dim;
+    const int j = (int)(i - t * dim);
+    const float v = z[i];
+    const float g = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    st(out + i, g * ld(table + (int64_t)tokens[t] * row_width + offset + j));
+}
+
+template <typename TOut>
+int stream_update(float* x, const float* delta, int splits, const float* scale, const float* rms_w, float rms_eps,
+                  const float* alpha, const float* w, const float* b, const int* rows, void* out, int n, int n_out, int width,
+                  cudaStream_t s) {
+    WICK_REQUIRE(width > 0 && n >= 0 && n_out >= 0 && splits >= 0, "stream_update: bad sizes");
+    WICK_REQUIRE((w == nullptr) == (b == nullptr) && (w == nullptr) == (alpha == nullptr), "stream_update: the norm's three tensors come together");
+    WICK_REQUIRE(!w || out, "stream_update: a norm needs a place for its result");
+    WICK_REQUIRE(delta || (!scale && !rms_w), "stream_update: nothing to scale or to norm");
+    if (n_out == 0) return 0;
+    const size_t smem = ((size_t)((width + 3) & ~3) + 40) * sizeof(float);
+    WICK_REQUIRE(smem <= 200 * 1024, "stream_update: width %d is beyond one block's shared memory", width);
+    static bool raised = false;
+    if (smem > 48 * 1024 && !raised) {
+        WICK_CUDA(cudaFuncSetAttribute(stream_update_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        raised = true;
+    }
+    const int threads = min(1024, max(64, ((width + 3) / 4 + 31) / 32 * 32));
+    WICK_CUDA(launch(stream_update_kernel<TOut>, dim3(n_out), dim3(threads), smem, s, x, delta, splits, (int64_t)n * width, scale,
+                     rms_w, rms_eps, alpha, w, b, rows, (TOut*)out, width));
+    return check_launch("stream_update");
+}
+
 template <typename TOut>
 int scaled_add_rmsnorm(float* x, const float* delta, int splits, float alpha, const float* w, float eps, void* out, int n,
                        int width, cudaStream_t s) {
@@ -148,6 +280,34 @@ WICK_API int wick_scaled_add_rmsnorm_bf16(float* x, const float* delta, int spli
 WICK_API int wick_scaled_add_rmsnorm_f32(float* x, const float* delta, int splits, float alpha, const float* w, float eps,
                                          void* out, int n, int width, void* s) {
     return scaled_add_rmsnorm<float>(x, delta, splits, alpha, w, eps, out, n, width, (cudaStream_t)s);
+}
+
+// x: float32 [n, width]; delta: float32 [splits, n, width] or null; scale, rms_w: float32 [width] or null; alpha [1], w, b
+// [width]: the tanh norm's tensors or null; rows: int32 [n_out] or null (then n_out = n); out: [n_out, width] or null.
+WICK_API int wick_stream_update_bf16(float* x, const float* delta, int splits, const float* scale, const float* rms_w,
+                                     float rms_eps, const float* alpha, const float* w, const float* b, const int* rows,
+                                     void* out, int n, int n_out, int width, void* s) {
+    return stream_update<bf16>(x, delta, splits, scale, rms_w, rms_eps, alpha, w, b, rows, out, n, n_out, width, (cudaStream_t)s);
+}
+WICK_API int wick_stream_update_f32(float* x, const float* delta, int splits, const float* scale, const float* rms_w,
+                                    float rms_eps, const float* alpha, const float* w, const float* b, const int* rows,
+                                    void* out, int n, int n_out, int width, void* s) {
+    return stream_update<float>(x, delta, splits, scale, rms_w, rms_eps, alpha, w, b, rows, out, n, n_out, width, (cudaStream_t)s);
+}
+
+WICK_API int wick_gelu_gate_rows_bf16(const float* z, const void* table, const int* tokens, void* out, int64_t n, int dim,
+                                      int64_t row_width, int offset, void* s) {
+    if (n == 0 || dim == 0) return 0;
+    WICK_CUDA(launch(gelu_gate_rows_kernel<bf16>, dim3(ceil_div(n * dim, 256)), dim3(256), 0, (cudaStream_t)s, z, (const bf16*)table,
+                     tokens, (bf16*)out, n, dim, row_width, offset));
+    return check_launch("gelu_gate_rows");
+}
+WICK_API int wick_gelu_gate_rows_f32(const float* z, const void* table, const int* tokens, void* out, int64_t n, int dim,
+                                     int64_t row_width, int offset, void* s) {
+    if (n == 0 || dim == 0) return 0;
+    WICK_CUDA(launch(gelu_gate_rows_kernel<float>, dim3(ceil_div(n * dim, 256)), dim3(256), 0, (cudaStream_t)s, z, (const float*)table,
+                     tokens, (float*)out, n, dim, row_width, offset));
+    return check_launch("gelu_gate_rows");
 }
 
 WICK_API int wick_relu_squared_bf16(void* a, int64_t n, void* s) {

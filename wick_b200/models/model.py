@@ -33,10 +33,14 @@ class Model:
             mixer_norm = build_part("norm", ls.mixer_norm, ctx)
             ffn = build_part("ffn", ls.ffn, ctx)
             ffn_norm = build_part("norm", ls.ffn_norm, ctx)
-            self.blocks.append(build_part("block", ls.block, ctx, mixer, mixer_norm, ffn, ffn_norm))
+            block = build_part("block", ls.block, ctx, mixer, mixer_norm, ffn, ffn_norm)
+            if ls.side is not None:
+                block.side = build_part("side", ls.side, ctx)
+            self.blocks.append(block)
         self.final_norm = build_part("norm", spec.final_norm, ctx)
         self.head = build_part("head", spec.head, ctx)
-        named = {"embedding": self.embedding, "final_norm": self.final_norm, "head": self.head}
+        self.shared = {sp.place: build_part(sp.category, sp.spec, ctx) for sp in spec.shared}
+        named = {"embedding": self.embedding, "final_norm": self.final_norm, "head": self.head, **self.shared}
         for _, part in self._places():
             if part.PEERS:
                 part.attach({k: named[k] for k in part.PEERS})
@@ -46,11 +50,15 @@ class Model:
     def _places(self) -> List[Tuple[str, Part]]:
         s = self.spec
         out: List[Tuple[str, Part]] = [(s.embedding_prefix, self.embedding)]
+        out += [(sp.prefix, self.shared[sp.place]) for sp in s.shared]
         for ls, blk in zip(s.layers, self.blocks):
             out += [(ls.prefix + ls.names["mixer_norm"], blk.mixer_norm),
                     (ls.prefix + ls.names["mixer"], blk.mixer),
                     (ls.prefix + ls.names["ffn_norm"], blk.ffn_norm),
-                    (ls.prefix + ls.names["ffn"], blk.ffn)]
+                    (ls.prefix + ls.names["ffn"], blk.ffn),
+                    (ls.prefix + ls.names.get("block", ""), blk)]
+            if blk.side is not None:
+                out.append((ls.prefix + ls.names.get("side", ""), blk.side))
         out += [(s.final_norm_prefix, self.final_norm), (s.head_prefix, self.head)]
         return out
 
@@ -108,6 +116,7 @@ class Model:
         for e in self.spec.schedule:
             b = self.blocks[e.layer]
             n += b.mixer.weight_bytes() + b.ffn.weight_bytes() + b.mixer_norm.weight_bytes() + b.ffn_norm.weight_bytes()
+            n += b.weight_bytes() + (b.side.weight_bytes() if b.side is not None else 0)
         return n
 
     def prompt_capturable(self) -> bool:
@@ -115,7 +124,7 @@ class Model:
         captured prompt step can be replayed for other prompts of the same padded size."""
         parts: List[Part] = [self.embedding, self.final_norm, self.head]
         for b in self.blocks:
-            parts += [b, b.mixer, b.mixer_norm, b.ffn, b.ffn_norm]
+            parts += [b, b.mixer, b.mixer_norm, b.ffn, b.ffn_norm] + ([b.side] if b.side is not None else [])
         return all(p.PROMPT_CAPTURABLE for p in parts)
 
     # ---- forward -------------------------------------------------------------
@@ -130,7 +139,9 @@ class Model:
             h = self.blocks[e.layer].forward(h, batch, cache.view(src, batch), e.read_cache_of is None)
         if batch.n_want == 0:
             return torch.empty((0, self.spec.vocab), dtype=torch.float32, device=self.ctx.device)
-        if h.pending is not None:
+        if h.pending is not None and (h.scale is not None or h.rms is not None):
+            xn = self.final_norm.add_forward(h.x, h.pending, self.ctx.dtype, batch.want, scale=h.scale, rms=h.rms)
+        elif h.pending is not None:
             xn = self.final_norm.add_forward(h.x, h.pending, self.ctx.dtype, batch.want)
         else:
             xn = self.final_norm.forward(h.x, self.ctx.dtype, batch.want)

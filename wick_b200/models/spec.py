@@ -30,8 +30,11 @@ class PartSpec:
 class LayerSpec:
     """One layer: an arrangement (``block``) of a mixer and a feed-forward, each
     with its norm.  ``prefix`` is the layer's tensor-name prefix; ``names`` maps
-    each place (``mixer``, ``mixer_norm``, ``ffn``, ``ffn_norm``) to the
-    sub-prefix its part's tensors are stored under."""
+    each place (``mixer``, ``mixer_norm``, ``ffn``, ``ffn_norm``, and ``block`` and
+    ``side`` where the layer has tensors there) to the sub-prefix its part's tensors
+    are stored under.  ``side`` is an optional part of the category ``side``: what the
+    layer adds to the stream after its feed-forward from something else than the
+    stream alone (a table row of the token, say)."""
 
     block: PartSpec
     mixer: PartSpec
@@ -40,6 +43,20 @@ class LayerSpec:
     ffn_norm: PartSpec
     prefix: str
     names: Mapping[str, str]
+    side: Optional[PartSpec] = None
+
+
+@dataclasses.dataclass(frozen=True)
+class SharedPart:
+    """A part that belongs to the model, not to a layer (a table that every layer reads a
+    slice of): parts that list ``place`` in their ``PEERS`` are handed it before the
+    weights load.  ``category`` and ``spec`` say what to build, ``prefix`` where its
+    tensors are stored."""
+
+    place: str
+    category: str
+    spec: PartSpec
+    prefix: str
 
 
 @dataclasses.dataclass(frozen=True)
@@ -67,6 +84,7 @@ class ModelSpec:
     head_prefix: str
     ignore_tensors: Tuple[str, ...] = ()   # fnmatch patterns of names a checkpoint may carry unused
     stop_token_ids: Tuple[int, ...] = ()
+    shared: Tuple[SharedPart, ...] = ()
 
     def validate(self) -> None:
         n = len(self.layers)

@@ -239,14 +239,14 @@ def add_delta(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
     return x
 
 
-def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-    """cos and sin of ``positions[t] * inv_freq[i]`` (float32 product), each [n, half]."""
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, amplitude: float = 1.0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos and sin of ``positions[t] * inv_freq[i]`` (float32 product), each [n, half], times ``amplitude``."""
     _cuda("positions", positions, torch.int32)
     _cuda("inv_freq", inv_freq, torch.float32)
     n, half = positions.numel(), inv_freq.numel()
     cos = torch.empty((n, half), dtype=torch.float32, device=positions.device)
     sin = torch.empty_like(cos)
-    _core().call("wick_rope_table", "ppppiip", _p(positions), _p(inv_freq), _p(cos), _p(sin), n, half, _stream())
+    _core().call("wick_rope_table", "ppppiifp", _p(positions), _p(inv_freq), _p(cos), _p(sin), n, half, float(amplitude), _stream())
     return cos, sin
 
 
@@ -522,7 +522,7 @@ def attention_decode_parts_fused(qkv: torch.Tensor, n_heads: int, n_kv: int, hea
 # Mechanisms of layers beyond the plain pre-norm decoder: the norm after the residual sum, a
 # feed-forward's squared ReLU, the soft cap of logits, attention with options (csrc/attn_masked.cu)
 # and experts chosen by a table (csrc/moe.cu).
-LAYER_SOURCES = ["layer_ops.cu", "attn_masked.cu", "moe.cu"]
+LAYER_SOURCES = ["layer_ops.cu", "attn_masked.cu", "attn_multi.cu", "moe.cu"]
 
 MASKS = {"causal": 0, "block": 1, "window": 2}
 PAIRINGS = {"neighbours": 0, "halves": 1}
@@ -587,17 +587,200 @@ def _kv_pages(name: str, kv: torch.Tensor, dtype, n_kv: int, d: int, e: int) -> 
           f"{name} must hold pages of {n_kv} x {PAGE} x ({d} + {e}) elements, is {tuple(kv.shape)}")
 
 
+def stream_update(x: torch.Tensor, delta: Optional[torch.Tensor], *, scale: Optional[torch.Tensor] = None,
+                  rms: Optional[Tuple[torch.Tensor, float]] = None, norm: Optional[tuple] = None,
+                  out_dtype: Optional[torch.dtype] = None, rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """The residual stream's own kernel.  ``x`` (float32 [n, width]) <- x + f(delta[0] + delta[1] + ...), in place:
+    f divides the sum by its root mean square and multiplies it by a weight (``rms`` = (weight, eps)), then
+    multiplies it by ``scale`` (float32 [width]), each where given.  With ``out_dtype`` the new rows also go out in
+    that type: after the norm ``("tanh", alpha, w, b)`` (tanh(alpha x) * w + b) if ``norm`` is given, else as they
+    are (for float32 that is ``x`` itself).  ``rows`` (int32 indices, a row may be named twice): only those rows go
+    out, and ``x`` itself is left as it was."""
+    _cuda("x", x, torch.float32)
+    n, width = x.shape
+    splits = 0
+    if delta is not None:
+        _cuda("delta", delta, torch.float32)
+        _need(delta.dim() == 3 and tuple(delta.shape[1:]) == (n, width),
+              f"delta must be [splits, {n}, {width}], is {tuple(delta.shape)}")
+        splits = delta.shape[0]
+    if scale is not None:
+        _cuda("scale", scale, torch.float32, (width,))
+    rms_w, rms_eps = (None, 0.0) if rms is None else rms
+    if rms_w is not None:
+        _cuda("rms weight", rms_w, torch.float32, (width,))
+    alpha = w = b = None
+    if norm is not None:
+        _need(norm[0] == "tanh" and out_dtype is not None, "the stream kernel knows the tanh norm, and a norm has a result type")
+        _, alpha, w, b = norm
+        _cuda("alpha", alpha, torch.float32, (1,))
+        _cuda("w", w, torch.float32, (width,))
+        _cuda("b", b, torch.float32, (width,))
+    if rows is not None:
+        _cuda("rows", rows, torch.int32)
+    n_out = n if rows is None else rows.numel()
+    out = None
+    if out_dtype is not None and not (norm is None and rows is None and out_dtype == torch.float32):
+        out = torch.empty((n_out, width), dtype=out_dtype, device=x.device)
+    if delta is None and out is None:
+        return x if out_dtype is not None else None
+    name = f"wick_stream_update_{_dt(out)}" if out is not None else "wick_stream_update_f32"
+    _layer().call(name, "ppippfpppppiiip", _p(x), _p(delta), splits, _p(scale), _p(rms_w), float(rms_eps),
+                  _p(alpha), _p(w), _p(b), _p(rows), _p(out), n, n_out, width, _stream())
+    if out is not None:
+        return out
+    return x if out_dtype is not None else None
+
+
+def gelu_gate_rows(z: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor, offset: int, dtype: torch.dtype) -> torch.Tensor:
+    """gelu(z[t, j]) * table[tokens[t], offset + j] in ``dtype``; gelu in its tanh form, float32.  z: float32 [n, dim]."""
+    _cuda("z", z, torch.float32)
+    _cuda("table", table, dtype)
+    _cuda("tokens", tokens, torch.int32)
+    n, dim = z.shape
+    _need(table.dim() == 2 and 0 <= offset and offset + dim <= table.shape[1], f"the table has no columns {offset} .. {offset + dim}")
+    _need(tokens.numel() == n, f"{n} rows and {tokens.numel()} tokens")
+    out = torch.empty((n, dim), dtype=dtype, device=z.device)
+    _layer().call(f"wick_gelu_gate_rows_{_dt(out)}", "pppplilip", _p(z), _p(table), _p(tokens), _p(out), n, dim, table.shape[1],
+                  int(offset), _stream())
+    return out
+
+
+ATTN_MULTI_MAX_V = 512      # the most numbers of a value row that attention_multi accumulates
+
+
+def attention_multi(q: torch.Tensor, store: torch.Tensor, batch, scale: float, *, maps: int, kv_heads: int, v_dim: int,
+                    window: int = 0, keep_first: int = 0, sink: Optional[torch.Tensor] = None,
+                    combine: Optional[Tuple[float, float, float]] = None, rows_of: Optional[int] = None,
+                    out_dtype: torch.dtype) -> torch.Tensor:
+    """Attention of the step's tokens over the cache (which already holds their own rows) with ``maps`` score maps
+    a head.  q: [n, H, maps * dm]; map a scores the a-th dm numbers of a key row and has a softmax of its own; all
+    maps weigh the same values.  Visible to the query at position p: with ``window`` > 0 the keys j <= p with
+    p - j < window or j < ``keep_first``, else every j <= p.  ``sink``: float32 [H], joins every map's denominator.
+
+    Two layouts of ``store``: pages of keys and values ([kv_heads][64][maps * dm] keys, then [kv_heads][64][v_dim]
+    values), or, with ``rows_of`` = R, pages of [64][R] rows whose first ``v_dim`` numbers are also the value
+    (one key head; maps * dm = R).
+
+    maps = 2 with ``combine`` = (lambda, eps, factor): the result is y = y_1 - lambda y_2, then
+    y / sqrt(mean(y^2) + eps) * factor over a head's values; q in the activation type.  maps = 1: q is float32 and
+    so is the result.  Returns [n, H, v_dim] in ``out_dtype``."""
+    _cuda("q", q)
+    n, H, d = q.shape
+    _need(maps in (1, 2) and d % maps == 0, f"a head of {d} numbers is not {maps} maps")
+    _need(n == batch.n_tokens, f"q has {n} rows, the batch {batch.n_tokens} tokens")
+    dm = d // maps
+    _cuda("store", store)
+    T = store.dtype
+    if rows_of is not None:
+        _need(kv_heads == 1 and d == rows_of and v_dim <= rows_of and store[0].numel() == PAGE * rows_of,
+              f"store must hold pages of {PAGE} rows of {rows_of} numbers, is {tuple(store.shape)}")
+        page_elems, k_row, v_off, v_row = PAGE * rows_of, rows_of, 0, rows_of
+    else:
+        _kv_pages("store", store, T, kv_heads, d, v_dim)
+        page_elems, k_row, v_off, v_row = kv_heads * PAGE * (d + v_dim), d, kv_heads * PAGE * d, v_dim
+    _need(v_dim <= ATTN_MULTI_MAX_V, f"values of {v_dim} numbers are beyond {ATTN_MULTI_MAX_V}")
+    if sink is not None:
+        _cuda("sink", sink, torch.float32, (H,))
+    if maps == 2:
+        _need(combine is not None and q.dtype == T and out_dtype == T, "two maps are combined, in the activation type")
+        name = f"wick_attn_multi2_{_dt(q)}"
+        lam, eps, factor = combine
+    else:
+        _need(q.dtype == torch.float32 and out_dtype == torch.float32, "one map takes and gives float32")
+        name = f"wick_attn_multi1_{'bf16' if T == torch.bfloat16 else 'f32'}"
+        lam, eps, factor = 0.0, 0.0, 1.0
+    out = torch.empty((n, H, v_dim), dtype=out_dtype, device=q.device)
+    few = 1 if n * H < 4 * 148 else 0
+    _layer().call(name, "ppppppiiiiiililifiipfffip", _p(q), _p(store), _p(out), _p(batch.seq_of_token), _p(batch.positions),
+                  _p(batch.page_table), batch.table_width, n, H, kv_heads, dm, v_dim, page_elems, k_row, v_off, v_row, float(scale),
+                  int(window), int(keep_first), _p(sink), float(lam), float(eps), float(factor), few, _stream())
+    return out
+
+
+def latent_finish(parts: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, gate_heads: int, *, dtype: torch.dtype,
+                  q_weight: torch.Tensor, kv_weight: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor],
+                  sin: Optional[torch.Tensor], pairing: str = "neighbours", rows: Optional[torch.Tensor],
+                  page_table: torch.Tensor, seq_of_token: torch.Tensor, positions: torch.Tensor):
+    """From the float32 partial sums ``parts`` [splits, n, q_rank + kv_rank + rot_dim + gate_heads] of a latent
+    attention's down-projections: the query latent rms(.) * q_weight -> [n, q_rank] in ``dtype``; the latent
+    rms(.) * kv_weight and the key part, turned by the angles of ``cos`` / ``sin`` [n, rot_dim / 2], -> the token's
+    row of ``rows`` (pages of [64][kv_rank + rot_dim]; None: nothing is stored); sigmoid of the gates -> float32
+    [n, gate_heads] (None if there are none).  Returns (query latent, gates)."""
+    _cuda("parts", parts, torch.float32)
+    W = q_rank + kv_rank + rot_dim + gate_heads
+    _need(parts.dim() == 3 and parts.shape[2] == W, f"parts must be [splits, n, {W}], is {tuple(parts.shape)}")
+    n = parts.shape[1]
+    _cuda("q_weight", q_weight, torch.float32, (q_rank,))
+    if kv_weight is not None:
+        _cuda("kv_weight", kv_weight, torch.float32, (kv_rank,))
+    if cos is not None:
+        _cuda("cos", cos, torch.float32, (n, rot_dim // 2) if rot_dim else None)
+        _cuda("sin", sin, torch.float32, (n, rot_dim // 2) if rot_dim else None)
+    if rows is not None:
+        _cuda("rows", rows, dtype)
+        _need(rows[0].numel() == PAGE * (kv_rank + rot_dim), f"rows must hold pages of {PAGE} x {kv_rank + rot_dim}, is {tuple(rows.shape)}")
+    _cuda("page_table", page_table, torch.int32)
+    _cuda("seq_of_token", seq_of_token, torch.int32, (n,))
+    _cuda("positions", positions, torch.int32, (n,))
+    cq = torch.empty((n, q_rank), dtype=dtype, device=parts.device)
+    gate = torch.empty((n, gate_heads), dtype=torch.float32, device=parts.device) if gate_heads else None
+    use_rot = cos is not None and rot_dim > 0
+    _layer().call(f"wick_latent_finish_{_dt(cq)}", "piiiiiippfppippppippp", _p(parts), parts.shape[0], n, q_rank, kv_rank, rot_dim,
+                  gate_heads, _p(q_weight), _p(kv_weight), float(eps), _p(cos) if use_rot else None, _p(sin) if use_rot else None,
+                  PAIRINGS[pairing], _p(cq), _p(gate), _p(rows), _p(page_table), page_table.shape[-1], _p(seq_of_token),
+                  _p(positions), _stream())
+    return cq, gate
+
+
+def latent_absorb(q_parts: torch.Tensor, uk: torch.Tensor, heads: int, d: int, rot_dim: int, kv_rank: int, *,
+                  cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], pairing: str = "neighbours") -> torch.Tensor:
+    """A latent attention's queries carried into the space of the cached rows.  ``q_parts``: float32 partial sums
+    [splits, n, heads * (d + rot_dim)], a head laid out as [d | rot_dim]; ``uk``: [heads * d, kv_rank].  Returns
+    float32 [n, heads, kv_rank + rot_dim]: [Wuk_h^T q_h[:d] | q_h[d:] turned by the angles]."""
+    _cuda("q_parts", q_parts, torch.float32)
+    W = heads * (d + rot_dim)
+    _need(q_parts.dim() == 3 and q_parts.shape[2] == W, f"q_parts must be [splits, n, {W}], is {tuple(q_parts.shape)}")
+    n = q_parts.shape[1]
+    _cuda("uk", uk, None, (heads * d, kv_rank))
+    use_rot = cos is not None and rot_dim > 0
+    if use_rot:
+        _cuda("cos", cos, torch.float32, (n, rot_dim // 2))
+        _cuda("sin", sin, torch.float32, (n, rot_dim // 2))
+    out = torch.empty((n, heads, kv_rank + rot_dim), dtype=torch.float32, device=q_parts.device)
+    _layer().call(f"wick_latent_absorb_{_dt(uk)}", "pipiiiiippipp", _p(q_parts), q_parts.shape[0], _p(uk), n, heads, d, rot_dim,
+                  kv_rank, _p(cos) if use_rot else None, _p(sin) if use_rot else None, PAIRINGS[pairing], _p(out), _stream())
+    return out
+
+
+def latent_expand(y: torch.Tensor, uv: torch.Tensor, gate: Optional[torch.Tensor], heads: int, v_dim: int, kv_rank: int, *,
+                  dtype: torch.dtype) -> torch.Tensor:
+    """out[t, h] = gate[t, h] * Wuv_h y[t, h].  y: float32 [n, heads, kv_rank] (a head's weighted sum of cached
+    latents); ``uv``: [heads * v_dim, kv_rank] in ``dtype``; gate: float32 [n, heads] or None.  Returns [n, heads * v_dim]."""
+    _cuda("y", y, torch.float32)
+    n = y.shape[0]
+    _need(tuple(y.shape) == (n, heads, kv_rank), f"y must be [n, {heads}, {kv_rank}], is {tuple(y.shape)}")
+    _cuda("uv", uv, dtype, (heads * v_dim, kv_rank))
+    if gate is not None:
+        _cuda("gate", gate, torch.float32, (n, heads))
+    out = torch.empty((n, heads * v_dim), dtype=dtype, device=y.device)
+    _layer().call(f"wick_latent_expand_{_dt(out)}", "pppiiiipp", _p(y), _p(uv), _p(gate), n, heads, v_dim, kv_rank, _p(out), _stream())
+    return out
+
+
+
 def qkv_finish(parts: torch.Tensor, n_heads: int, n_kv: int, d: int, e: int, *, dtype: torch.dtype,
                bias: Optional[torch.Tensor] = None, q_weight: Optional[torch.Tensor] = None,
                k_weight: Optional[torch.Tensor] = None, eps: float = 0.0, cos: Optional[torch.Tensor] = None,
-               sin: Optional[torch.Tensor] = None, rot_dims: int = 0, pairing: str = "neighbours", v_keep: Optional[torch.Tensor] = None, v_mode: int = 0,
+               sin: Optional[torch.Tensor] = None, rot_dims: int = 0, pairing: str = "neighbours", maps: int = 1,
+               v_keep: Optional[torch.Tensor] = None, v_mode: int = 0,
                blend: Optional[torch.Tensor] = None, kv: Optional[torch.Tensor], page_table: torch.Tensor,
                seq_of_token: torch.Tensor, positions: torch.Tensor, write_kv: bool = True) -> torch.Tensor:
     """From the q/k/v projection's float32 partial sums ``parts`` [splits, n, H d + G d + G e]:
     biases, RMS norms of q and k over spans the length of their weight vectors (a head, or the
     whole projection), rotation of the first ``rot_dims`` elements of every q and k head by the
     angles whose ``cos`` and ``sin`` [n, rot_dims / 2] are given (``pairing``: which two elements
-    turn together), the value blend
+    turn together; ``maps``: a head is that many vectors side by side, each turned on its own), the value blend
     (``v_mode`` 1: the values are also kept in ``v_keep`` [n, G e]; 2: v <- (1 - blend) v + blend
     v_keep), then q -> the result [n, H, d] in ``dtype`` and k, v -> the token's place in ``kv``."""
     _cuda("parts", parts, torch.float32)
@@ -627,9 +810,10 @@ def qkv_finish(parts: torch.Tensor, n_heads: int, n_kv: int, d: int, e: int, *, 
     _cuda("seq_of_token", seq_of_token, torch.int32, (n,))
     _cuda("positions", positions, torch.int32, (n,))
     q_out = torch.empty((n, n_heads, d), dtype=dtype, device=parts.device)
-    _layer().call(f"wick_qkv_finish_{_dt(q_out)}", "piipiiiipipifppiipippppippip", _p(parts), parts.shape[0], n, _p(bias),
+    _need(maps >= 1 and d % maps == 0, f"a head of {d} numbers is not {maps} vectors")
+    _layer().call(f"wick_qkv_finish_{_dt(q_out)}", "piipiiiipipifppiiipippppippip", _p(parts), parts.shape[0], n, _p(bias),
                   n_heads, n_kv, d, e, _p(q_weight), q_span, _p(k_weight), k_span, float(eps), _p(cos), _p(sin),
-                  rot_dims if cos is not None else 0, PAIRINGS[pairing], _p(v_keep), v_mode, _p(blend), _p(q_out),
+                  rot_dims if cos is not None else 0, PAIRINGS[pairing], int(maps), _p(v_keep), v_mode, _p(blend), _p(q_out),
                   _p(kv) if write_kv else None, _p(page_table), page_table.shape[-1], _p(seq_of_token), _p(positions),
                   1 if write_kv else 0, _stream())
     return q_out

@@ -7,7 +7,10 @@ position       ``rotary_pairs``        head_dim, dims (rotated elements of each
                                        head, from the first; default head_dim),
                                        theta, pairing (``neighbours``: elements
                                        2i and 2i+1 turn together; ``halves``:
-                                       i and i + dims/2)
+                                       i and i + dims/2), scaling (None, or
+                                       {"kind": "wavelength", factor, low, high,
+                                       original}, or {"kind": "ramp", factor,
+                                       original, fast, slow})
 mixer          ``attention``           width, heads, kv_heads, head_dim, v_dim
                                        (default head_dim), bias, scale,
                                        qk_norm (None, ``head`` or ``projection``),
@@ -42,7 +45,8 @@ and v, which have the compute dtype.
 """
 from __future__ import annotations
 
-from typing import Optional
+import math
+from typing import List, Optional, Tuple
 
 import torch
 
@@ -53,10 +57,50 @@ from .linear import Linear
 from .standard import NoPosition
 
 
+def scaled_frequencies(dims: int, theta: float, scaling) -> Tuple[List[float], float]:
+    """The frequencies f_i = theta^(-2i/dims), i < dims/2, changed by ``scaling``, and the
+    factor of cos and sin (1 unless the scaling has one); float64 arithmetic.
+
+    ``wavelength`` (the Llama 3.1 rule): with l = 2 pi / f, a frequency stays where
+    l < original / high, is divided by ``factor`` where l > original / low, and between the
+    two is (1 - s) f / factor + s f with s = (original / l - low) / (high - low).
+
+    ``ramp`` (the YaRN rule): with index(t) = dims ln(original / (2 pi t)) / (2 ln theta),
+    lo = max(floor(index(fast)), 0), hi = min(ceil(index(slow)), dims - 1) and
+    r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the frequency becomes
+    f_i / factor * r_i + f_i (1 - r_i), and cos and sin are multiplied by 0.1 ln(factor) + 1."""
+    freqs = [theta ** (-2.0 * i / dims) for i in range(dims // 2)]
+    if not scaling:
+        return freqs, 1.0
+    sc, kind = dict(scaling), dict(scaling).get("kind")
+    if kind == "wavelength":
+        out = []
+        for f in freqs:
+            l = 2.0 * math.pi / f
+            if l > sc["original"] / sc["low"]:
+                f = f / sc["factor"]
+            elif l >= sc["original"] / sc["high"]:
+                t = (sc["original"] / l - sc["low"]) / (sc["high"] - sc["low"])
+                f = (1.0 - t) * f / sc["factor"] + t * f
+            out.append(f)
+        return out, 1.0
+    if kind == "ramp":
+        def index(turns):
+            return dims * math.log(sc["original"] / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+        lo, hi = max(math.floor(index(sc["fast"])), 0), min(math.ceil(index(sc["slow"])), dims - 1)
+        out = []
+        for i, f in enumerate(freqs):
+            r = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+            out.append(f / sc["factor"] * r + f * (1.0 - r))
+        return out, 0.1 * math.log(sc["factor"]) + 1.0
+    raise ValueError(f"unknown frequency scaling {kind!r} (wavelength, ramp)")
+
+
 class RotaryPairs(Position):
     """Pairs of the first ``dims`` elements of every head turn by ``position * theta^(-2i/dims)``,
-    i counting the pairs; the other elements pass.  The frequencies are evaluated in float64
-    and rounded to float32 once; the angle is their float32 product with the position."""
+    i counting the pairs; the other elements pass.  The frequencies (after ``scaling``, see
+    :func:`scaled_frequencies`) are evaluated in float64 and rounded to float32 once; the angle
+    is their float32 product with the position."""
 
     PROMPT_CAPTURABLE = True
 
@@ -70,7 +114,9 @@ class RotaryPairs(Position):
             raise ValueError(f"unknown pairing {self.pairing} ({', '.join(ops.PAIRINGS)})")
         if self.dims % 2 != 0 or not 0 < self.dims <= self.head_dim:
             raise ValueError(f"{self.dims} rotated elements of a head of {self.head_dim}")
-        inv = [self.theta ** (-2.0 * i / self.dims) for i in range(self.dims // 2)]
+        sc = params.get("scaling")
+        self.scaling = tuple(sorted(dict(sc).items())) if sc else ()
+        inv, self.amplitude = scaled_frequencies(self.dims, self.theta, sc)
         self.inv_freq = torch.tensor(inv, dtype=torch.float64).to(torch.float32).to(ctx.device)
 
     def rotary_inv_freq(self):
@@ -78,14 +124,14 @@ class RotaryPairs(Position):
 
     def tables(self, batch):
         """cos/sin [tokens, dims/2] of this step, computed once and shared by every layer that turns alike."""
-        key = ("rotary_pairs", self.dims, self.theta)
+        key = ("rotary_pairs", self.dims, self.theta, self.scaling)
         t = batch.memo.get(key)
         if t is None:
-            t = batch.memo[key] = ops.rope_table(batch.positions, self.inv_freq)
+            t = batch.memo[key] = ops.rope_table(batch.positions, self.inv_freq, self.amplitude)
         return t
 
     def apply(self, q, k, positions):
-        cos, sin = ops.rope_table(positions, self.inv_freq)
+        cos, sin = ops.rope_table(positions, self.inv_freq, self.amplitude)
         half = self.dims // 2
         for x in (q, k):
             r = x[..., :self.dims]

@@ -2,7 +2,9 @@
 
 Categories: ``mixer`` (token mixing over the sequence: attention here),
 ``ffn`` (feed-forward), ``norm``, ``position`` (position encoding), ``block``
-(the arrangement of the former in one layer), ``embedding`` and ``head``.
+(the arrangement of the former in one layer), ``side`` (what a layer adds to the
+stream after its feed-forward from something else than the stream alone),
+``embedding`` and ``head``.
 
 A part is built from a :class:`~wick_b200.models.spec.PartSpec` — its registered
 kind plus its sizes and constants — and a :class:`BuildContext` (compute dtype
@@ -25,7 +27,7 @@ import torch
 
 from ..models.spec import PartSpec
 
-CATEGORIES = ("mixer", "ffn", "norm", "position", "block", "embedding", "head")
+CATEGORIES = ("mixer", "ffn", "norm", "position", "block", "side", "embedding", "head")
 
 
 @dataclasses.dataclass(frozen=True)
@@ -80,8 +82,9 @@ class CacheNeed:
 
     kind ``paged_kv``: keys and values of every position, ``kv_heads`` x
     ``head_dim`` each, in pages (values ``v_head_dim`` each, if that is given and
-    differs); ``window`` (tokens) if only the last ones are ever read.  kind ``state``: one record of fixed ``shape`` and ``dtype`` per
-    sequence, zeroed when the sequence starts."""
+    differs); ``window`` (tokens) if only the last ones are ever read.  kind ``paged_rows``:
+    one row of ``shape`` per position, in the same pages.  kind ``state``: one record of fixed
+    ``shape`` and ``dtype`` per sequence, zeroed when the sequence starts."""
 
     kind: str
     kv_heads: int = 0
@@ -142,12 +145,18 @@ class Norm(Part):
         raise NotImplementedError
 
     def add_forward(self, x: torch.Tensor, delta: torch.Tensor, out_dtype: torch.dtype,
-                    rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    rows: Optional[torch.Tensor] = None, *, scale: Optional[torch.Tensor] = None,
+                    rms: Optional[Tuple[torch.Tensor, float]] = None) -> torch.Tensor:
         """``x += sum(delta)`` in float32 and in place (``delta`` is
         [splits, n, width], summed in index order), then normalise.  With
         ``rows`` only those rows are normalised and ``x`` need not be brought up
-        to date (nobody reads it afterwards)."""
-        x.add_(delta.sum(0) if delta.shape[0] > 1 else delta[0])
+        to date (nobody reads it afterwards).  ``scale`` (float32 [width]): the
+        sum is multiplied by it element by element before it is added; ``rms``
+        (weight, eps): the sum is divided by its root mean square and multiplied
+        by the weight first.  A norm without a kernel for these resolves the sum
+        into ``x`` with the stream kernel and normalises then."""
+        from .. import ops
+        ops.stream_update(x, delta, scale=scale, rms=rms)
         return self.forward(x, out_dtype, rows)
 
     def scaled_add_forward(self, x: torch.Tensor, delta: Optional[torch.Tensor], alpha: float,
@@ -208,20 +217,38 @@ class FeedForward(Part):
 class Hidden:
     """The residual stream between blocks: float32 ``x`` [tokens, width] and a
     float32 ``pending`` [splits, tokens, width] that has still to be added to it
-    (kept apart so that the next norm's kernel can do the addition).  ``act`` is ``x``
-    in the compute dtype where a block has made that copy (blocks whose sublayers read
-    the stream itself), else None."""
+    (kept apart so that the next norm's kernel can do the addition).  ``scale``
+    (float32 [width]) is a factor, element by element, of the pending sum; ``rms``
+    (weight, eps) says that the pending sum is divided by its root mean square and
+    multiplied by the weight before it is added; both are None for a plain sum.  ``act``
+    is ``x`` in the compute dtype where a block has made that copy (blocks whose
+    sublayers read the stream itself), else None."""
 
-    __slots__ = ("x", "pending", "act")
+    __slots__ = ("x", "pending", "act", "scale", "rms")
 
     def __init__(self, x: torch.Tensor, pending: Optional[torch.Tensor] = None):
         self.x, self.pending, self.act = x, pending, None
+        self.scale: Optional[torch.Tensor] = None
+        self.rms: Optional[Tuple[torch.Tensor, float]] = None
 
-    def resolved(self) -> torch.Tensor:
-        if self.pending is not None:
+    def defer(self, delta: Optional[torch.Tensor], scale: Optional[torch.Tensor] = None,
+              rms: Optional[Tuple[torch.Tensor, float]] = None) -> None:
+        """Leave ``delta`` (None: nothing) to be added by whoever reads the stream next."""
+        self.pending, self.scale, self.rms = delta, (scale if delta is not None else None), (rms if delta is not None else None)
+
+    def resolved(self, act_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """The stream with everything added; with ``act_dtype`` its copy in that type is
+        made on the way and left in ``act``."""
+        from .. import ops
+        if self.pending is not None and (self.scale is not None or self.rms is not None or act_dtype is not None):
+            self.act = ops.stream_update(self.x, self.pending, scale=self.scale, rms=self.rms, out_dtype=act_dtype)
+            self.defer(None)
+        elif self.pending is not None:
             p = self.pending
             self.x.add_(p.sum(0) if p.shape[0] > 1 else p[0])
             self.pending = None
+        elif act_dtype is not None and self.act is None:
+            self.act = ops.to_activation(self.x, act_dtype)
         return self.x
 
 
@@ -231,8 +258,20 @@ class Block(Part):
     def __init__(self, params, ctx, mixer: Mixer, mixer_norm: Norm, ffn: FeedForward, ffn_norm: Norm):
         super().__init__(params, ctx)
         self.mixer, self.mixer_norm, self.ffn, self.ffn_norm = mixer, mixer_norm, ffn, ffn_norm
+        self.side: Optional["SideInput"] = None        # set by the model where the layer's spec names one
 
     def forward(self, h: Hidden, batch: "Any", cache: "Any", write_cache: bool) -> Hidden:
+        raise NotImplementedError
+
+
+class SideInput(Part):
+    """What a layer adds to the stream after its feed-forward from something else than
+    the stream alone."""
+    category = "side"
+
+    def forward(self, h: Hidden, batch: "Any") -> None:
+        """``h`` comes with everything of the layer added or pending; the part leaves
+        its own addition in ``h`` (added, or pending through :meth:`Hidden.defer`)."""
         raise NotImplementedError
 
 

@@ -1,0 +1,79 @@
+"""What a layer adds to the stream from the token ids.
+
+=============  ======================  ==========================================
+category       kind                    params
+=============  ======================  ==========================================
+side           ``gated_token_rows``    width, dim, offset, eps, table (the place
+                                       of the model's shared table part), names
+                                       (gate, proj, norm -> local names)
+=============  ======================  ==========================================
+
+With x the stream after the layer's feed-forward and e the ``dim`` numbers from ``offset``
+on of the token's row in the shared table:  g = gelu(Wgate x) * e  (gelu in its tanh
+form), y = Wproj g, and x <- x + y / sqrt(mean(y^2) + eps) * w.  The gate reads the stream
+itself, so the layer's pending sum is resolved first; the part's own sum stays pending,
+with the norm, for whoever reads the stream next.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import SideInput, TensorSpec, register_part
+from .linear import Linear
+
+
+class GatedTokenRows(SideInput):
+    PROMPT_CAPTURABLE = True
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.width, self.dim, self.offset = int(params["width"]), int(params["dim"]), int(params["offset"])
+        self.eps = float(params["eps"])
+        self.table_place = str(params["table"])
+        self.PEERS = (self.table_place,)
+        names = dict(gate="gate.weight", proj="proj.weight", norm="norm.weight")
+        names.update(params.get("names") or {})
+        self.names = names
+        self.gate = Linear(self.dim, self.width, ctx)
+        self.proj = Linear(self.width, self.dim, ctx)
+        self.norm_weight = None
+        self.table = None
+
+    def attach(self, peers):
+        self.table = peers[self.table_place]
+
+    def tensor_specs(self):
+        nm = self.names
+        return [TensorSpec(nm["gate"], (self.dim, self.width)), TensorSpec(nm["proj"], (self.width, self.dim)),
+                TensorSpec(nm["norm"], (self.width,), "vector")]
+
+    def load(self, fetch):
+        nm = self.names
+        self.gate.load_rows([fetch(nm["gate"])])
+        self.proj.load_rows([fetch(nm["proj"])])
+        self.norm_weight = self.ctx.hold(fetch(nm["norm"]), "vector")
+        rows = self.table.tensor("weight")
+        if rows is None or rows.shape[1] < self.offset + self.dim:
+            raise ValueError(f"the shared table has no columns {self.offset} .. {self.offset + self.dim}")
+
+    def tensor(self, name):
+        nm = self.names
+        if name == nm["gate"]:
+            return self.gate.rows(0, self.dim)
+        if name == nm["proj"]:
+            return self.proj.rows(0, self.width)
+        return self.norm_weight if name == nm["norm"] else None
+
+    def weight_bytes(self):
+        return self.gate.weight_bytes() + self.proj.weight_bytes() + 4 * self.width
+
+    def forward(self, h, batch):
+        dt = self.ctx.dtype
+        h.resolved(dt)                                               # x with the layer's sums, and its copy in h.act
+        z = self.gate.forward(h.act, torch.float32)                  # [n, dim]
+        g = ops.gelu_gate_rows(z, self.table.tensor("weight"), batch.tokens, self.offset, dt)
+        h.defer(self.proj.forward_delta(g), rms=(self.norm_weight, self.eps))
+
+
+register_part("side", "gated_token_rows", GatedTokenRows)

@@ -8,6 +8,8 @@ category       kind                    params
 norm           ``rms``                 width, eps, offset (added to the stored
                                        weight, default 0), tensor (its local
                                        name, default "weight"), optional
+norm           ``tanh``                width, tensor, names (bias, alpha ->
+                                       local names), optional
 position       ``rotary_half_split``   head_dim, theta
 position       ``none``                —
 mixer          ``gqa_attention``       width, heads, kv_heads, head_dim,
@@ -15,7 +17,9 @@ mixer          ``gqa_attention``       width, heads, kv_heads, head_dim,
                                        position (PartSpec), scale (or None)
 ffn            ``gated_mlp``           width, intermediate, activation ("silu"),
                                        names (gate, up, down -> local names)
-block          ``prenorm_residual``    —
+block          ``prenorm_residual``    width and layer_scale (mixer, ffn -> local
+                                       names of the two factors) where the
+                                       sublayers' results are scaled
 block          ``postnorm_residual``   alpha
 embedding      ``table``               vocab, width, tensor
 head           ``linear``              vocab, width, tied, tensor, soft_cap
@@ -84,7 +88,9 @@ class RMSNorm(Norm):
     def forward(self, x, out_dtype, rows=None):
         return ops.rmsnorm(x, self.weight, self.eps, out_dtype, rows=rows)
 
-    def add_forward(self, x, delta, out_dtype, rows=None):
+    def add_forward(self, x, delta, out_dtype, rows=None, *, scale=None, rms=None):
+        if scale is not None or rms is not None:
+            return super().add_forward(x, delta, out_dtype, rows, scale=scale, rms=rms)
         return ops.rmsnorm(x, self.weight, self.eps, out_dtype, delta=delta, rows=rows)
 
     def scaled_add_forward(self, x, delta, alpha, out_dtype):
@@ -92,6 +98,62 @@ class RMSNorm(Norm):
 
     def weight_bytes(self):
         return self.width * 4
+
+
+class TanhNorm(Norm):
+    """tanh(alpha x) * w + b with one learned number alpha: a norm that computes no mean and
+    no variance.  Evaluated in float32.  The three tensors are stored under ``tensor`` (w)
+    and the local names ``names`` gives for ``bias`` and ``alpha``."""
+
+    PROMPT_CAPTURABLE = True
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.width = int(params["width"])
+        self.name = str(params.get("tensor", "weight"))
+        names = dict(bias="bias", alpha="alpha")
+        names.update(params.get("names") or {})
+        self.names = names
+        self.optional = bool(params.get("optional", False))
+        self.weight = self.bias = self.alpha = None
+
+    @property
+    def present(self) -> bool:
+        return self.weight is not None
+
+    def tensor_specs(self):
+        o, init = self.optional, ("absent" if self.optional else "")
+        return [TensorSpec(self.name, (self.width,), "vector", optional=o, init=init),
+                TensorSpec(self.names["bias"], (self.width,), "vector", optional=o, init=init or "around_zero"),
+                TensorSpec(self.names["alpha"], (), "vector", optional=o, init=init or "unit_interval")]
+
+    def load(self, fetch):
+        w = fetch(self.name)
+        if w is None and self.optional:
+            self.weight = self.bias = self.alpha = None
+            return
+        hold = self.ctx.hold
+        self.weight, self.bias = hold(w, "vector"), hold(fetch(self.names["bias"]), "vector")
+        self.alpha = hold(fetch(self.names["alpha"]), "vector").reshape(1)
+
+    def tensor(self, name):
+        if name == self.name:
+            return self.weight
+        if name == self.names["bias"]:
+            return self.bias
+        return self.alpha.reshape(()) if name == self.names["alpha"] and self.alpha is not None else None
+
+    def _norm(self):
+        return ("tanh", self.alpha, self.weight, self.bias)
+
+    def forward(self, x, out_dtype, rows=None):
+        return ops.stream_update(x, None, norm=self._norm(), out_dtype=out_dtype, rows=rows)
+
+    def add_forward(self, x, delta, out_dtype, rows=None, *, scale=None, rms=None):
+        return ops.stream_update(x, delta, scale=scale, rms=rms, norm=self._norm(), out_dtype=out_dtype, rows=rows)
+
+    def weight_bytes(self):
+        return (2 * self.width + 1) * 4
 
 
 # ---------------------------------------------------------------------------
@@ -319,27 +381,72 @@ class PreNormResidual(Block):
     """x += mixer(norm1(x)); x += ffn(norm2(x)).  An addition is either left pending,
     so that the following norm's kernel performs it, or done by the part itself: a
     part whose class says ``ADDS_TO_RESIDUAL`` is handed the residual stream and
-    returns None when it has added its result to it (its last kernel did)."""
+    returns None when it has added its result to it (its last kernel did).
+
+    ``layer_scale`` (the local names of two float32 vectors of ``width`` numbers): the
+    mixer's and the feed-forward's results are multiplied by them, element by element,
+    before the sum; the factor travels with the pending sum, and the parts never add to
+    the stream themselves.  A layer whose feed-forward is of kind ``none`` ends after its
+    mixer.  A ``side`` part, if the layer has one, runs last."""
 
     PROMPT_CAPTURABLE = True
+
+    def __init__(self, params, ctx, mixer, mixer_norm, ffn, ffn_norm):
+        super().__init__(params, ctx, mixer, mixer_norm, ffn, ffn_norm)
+        self.scale_names = dict(params.get("layer_scale") or {})
+        self.width = int(params["width"]) if self.scale_names else 0
+        self.scales = {}
+
+    def tensor_specs(self):
+        no_ffn = getattr(self.ffn, "IS_NONE", False)
+        return [TensorSpec(nm, (self.width,), "vector", optional=(k == "ffn" and no_ffn), init="absent" if k == "ffn" and no_ffn else "")
+                for k, nm in self.scale_names.items()]
+
+    def load(self, fetch):
+        for k, nm in self.scale_names.items():
+            t = fetch(nm)
+            self.scales[k] = None if t is None else self.ctx.hold(t, "vector")
+
+    def tensor(self, name):
+        for k, nm in self.scale_names.items():
+            if nm == name:
+                return self.scales.get(k)
+        return None
+
+    def weight_bytes(self):
+        return sum(4 * self.width for v in self.scales.values() if v is not None)
 
     def forward(self, h, batch, cache, write_cache):
         dt = self.ctx.dtype
         h.act = None                     # (this block changes the stream without keeping a copy)
-        if h.pending is not None:
+        scaled = bool(self.scale_names)
+        if h.pending is not None and (h.scale is not None or h.rms is not None):
+            xn = self.mixer_norm.add_forward(h.x, h.pending, dt, scale=h.scale, rms=h.rms)
+        elif h.pending is not None:
             xn = self.mixer_norm.add_forward(h.x, h.pending, dt)
         else:
             xn = self.mixer_norm.forward(h.x, dt)
-        if getattr(self.mixer, "ADDS_TO_RESIDUAL", False):
+        h.defer(None)
+        if getattr(self.mixer, "ADDS_TO_RESIDUAL", False) and not scaled:
             d = self.mixer.forward(xn, batch, cache, write_cache, residual=h.x)
         else:
             d = self.mixer.forward(xn, batch, cache, write_cache)
-        xn = self.ffn_norm.forward(h.x, dt) if d is None else self.ffn_norm.add_forward(h.x, as_splits(d), dt)
-        if getattr(self.ffn, "ADDS_TO_RESIDUAL", False):
-            d = self.ffn.forward(xn, batch, residual=h.x)
+        if getattr(self.ffn, "IS_NONE", False):
+            h.defer(None if d is None else as_splits(d), self.scales.get("mixer"))
         else:
-            d = self.ffn.forward(xn, batch)
-        h.pending = None if d is None else as_splits(d)
+            if d is None:
+                xn = self.ffn_norm.forward(h.x, dt)
+            elif scaled:
+                xn = self.ffn_norm.add_forward(h.x, as_splits(d), dt, scale=self.scales.get("mixer"))
+            else:
+                xn = self.ffn_norm.add_forward(h.x, as_splits(d), dt)
+            if getattr(self.ffn, "ADDS_TO_RESIDUAL", False) and not scaled:
+                d = self.ffn.forward(xn, batch, residual=h.x)
+            else:
+                d = self.ffn.forward(xn, batch)
+            h.defer(None if d is None else as_splits(d), self.scales.get("ffn"))
+        if self.side is not None:
+            self.side.forward(h, batch)
         return h
 
 
@@ -448,6 +555,7 @@ class LinearHead(Head):
 
 
 register_part("norm", "rms", RMSNorm)
+register_part("norm", "tanh", TanhNorm)
 register_part("position", "rotary_half_split", RotaryHalfSplit)
 register_part("position", "none", NoPosition)
 register_part("mixer", "gqa_attention", GQAttention)
