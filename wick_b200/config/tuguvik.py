@@ -170,16 +170,16 @@ class TuguvikConfig(ModelConfig):
         D, n = self.width, 2 * self.vocab_size * self.width + 2 * self.width + 1
         for L in self.layers:
             m = L.mixer
-            n += 2 * (2 * D + 1) + D
+            n += (2 * D + 1) + D
             if L.type == "attention":
                 n += D * (2 * m.dim * (m.heads + m.kv_heads) + m.kv_heads * m.vdim + m.heads * m.vdim) + 4 * m.dim
             else:
                 n += D * m.q_rank + m.q_rank + m.q_rank * m.heads * (m.dim + m.rot_dim) + m.kv_rank * m.heads * (m.dim + m.vdim)
-                n += 2 * m.heads + m.heads * D + D * m.heads * m.vdim
+                n += m.heads + m.heads * D + D * m.heads * m.vdim
                 if m.kv_from is None:
                     n += D * (m.kv_rank + m.rot_dim) + m.kv_rank
             if L.ff is not None:
-                n += 3 * D * L.ff + D
+                n += 3 * D * L.ff + D + (2 * D + 1)
             if self.side_dim:
                 n += self.vocab_size * self.side_dim + 2 * D * self.side_dim + D
         return n
