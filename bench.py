@@ -2,7 +2,7 @@
 """Decode and prefill throughput of wick_b200 on one B200, as one JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--model 8b|14b|32b]
-    python bench.py --design nibotar [--design-size 2k|4k]      (a line of its own, see below)
+    python bench.py --design nibotar|tuguvik [--design-size 2k|4k]      (a line of its own, see below)
 
 The default run has the layer sizes of Qwen3-8B (36 layers, hidden 4096, 32
 heads over 8 kv heads of 128, intermediate 12288, vocabulary 151936) with random
@@ -31,6 +31,10 @@ Nibotar token's experts and shared expert add up to), and ``parts``: where a pro
 a decode step of each spend their time, per kind of kernel, with the fraction of the
 measured peak each reaches (a second process times them with CUDA events around every call,
 launched one by one without programmatic dependent launch, so that they do not overlap).
+``--design tuguvik`` does the same for the Tuguvik design (layers of differential attention
+and of attention through a cached latent, every layer with a gated feed-forward of Qwen3's
+intermediate size and a token input); its ``parts`` count each kernel's own arithmetic and
+bytes, so that every kind can be held against the measured peaks.
 """
 import argparse
 import json
@@ -257,6 +261,8 @@ def design_step_bytes(eng, z, name, batch, kv_tokens):
         used = e * (1.0 - (1.0 - top / e) ** batch)
         n += (z["layers"] - 1) * (used - top) * one
         kv_tokens = min(kv_tokens, batch * z["mask"])
+    if name == "tuguvik":
+        kv_tokens = min(kv_tokens, batch * (z["window"] + z["keep_first"]))
     return n + eng.cache.read_bytes(int(kv_tokens), batch)
 
 
@@ -411,6 +417,185 @@ def design_compare(args) -> int:
     return 0 if all(m["finite"] for m in models.values()) else 1
 
 
+# ---- --design tuguvik ----------------------------------------------------------
+# Layer sizes: differential attention with as many numbers a head as Qwen3 (two maps of 64), attention through a latent
+# of 512 + 64 numbers a position with heads of 128 + 64 query numbers and 128 values; windows; a gated feed-forward.
+TUGUVIK_SIZES = {
+    "2k": dict(width=2048, heads=16, kv=4, dim=128, layers=8, vocab=32768, window=1024, keep_first=4, ff=5120, q_rank=768,
+               kv_rank=512, rot_dim=64, side=256),
+    "4k": dict(width=4096, heads=32, kv=8, dim=128, layers=4, vocab=32768, window=2048, keep_first=4, ff=10240, q_rank=1536,
+               kv_rank=512, rot_dim=64, side=256),
+}
+
+
+def tuguvik_configs(z):
+    d = z["dim"]
+    diff = dict(heads=z["heads"], kv_heads=z["kv"], dim=d // 2, vdim=d, scale=(d // 2) ** -0.5, diff=0.8,
+                mask={"size": z["window"], "keep_first": z["keep_first"]},
+                rot={"dims": d // 2, "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}})
+
+    def latent(src):
+        m = dict(heads=z["heads"], dim=d, rot_dim=z["rot_dim"], vdim=d, q_rank=z["q_rank"], kv_rank=z["kv_rank"],
+                 scale=(d + z["rot_dim"]) ** -0.5, mask={"size": z["window"]},
+                 rot={"dims": z["rot_dim"], "base": 10000.0, "scaling": {"factor": 40.0, "fast": 32.0, "slow": 1.0, "original": 4096}})
+        if src is not None:
+            m["kv_from"] = src
+        return m
+    layers = []
+    for i in range(z["layers"]):                      # differential, latent, latent on the same rows, differential, ...
+        kind = (0, 1, 2, 0)[i % 4]
+        mixer = diff if kind == 0 else latent(None if kind == 1 else i - 1)
+        layers.append(dict(type="attention" if kind == 0 else "latent_attention", mixer=mixer, mlp={"kind": "dense", "ff": z["ff"]}))
+    tug = dict(architecture="Tuguvik", vocab=z["vocab"], width=z["width"], norm={"eps": 1e-5}, token_side={"dim": z["side"]},
+               layers=layers)
+    qwen = _qwen3(z["width"], z["heads"], z["kv"], z["ff"], z["layers"])
+    qwen.update(head_dim=d, vocab_size=z["vocab"])
+    return {"tuguvik": tug, "qwen3": qwen}
+
+
+def tuguvik_parts(torch, wick, pk, z, name, cfg_json):
+    """What a 2,048-token prompt step and a decode step of 8 sequences (1,500 cached positions each) spend in each kind of
+    kernel: microseconds a step (all layers), and the kernels' own arithmetic and bytes over that time against the measured
+    peaks.  Every call of a kernel's Python face is timed with CUDA events and says what it computes and moves."""
+    from wick_b200 import ops
+    from wick_b200.parts.linear import Linear
+    cfg = wick.config_from_json(cfg_json)
+    eng = wick.Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=8 * 1600 + PREFILL + 64, use_graphs=False)
+    acc = {}
+    ctx = {"pairs": 0, "kv_rows": 0}
+
+    def timed(kind, fn, work):
+        def run(*a, **kw):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(torch.cuda.current_stream())
+            r = fn(*a, **kw)
+            e1.record(torch.cuda.current_stream())
+            acc.setdefault(kind, []).append((e0, e1) + tuple(work(r, *a, **kw)))
+            return r
+        return run
+
+    def nbytes(*ts):
+        return sum(t.numel() * t.element_size() for t in ts if t is not None)
+
+    def product(kind, lin):
+        w = lin.out_features * lin.in_features
+        n_out = lin.out_features // 2 if lin.gated else lin.out_features
+        for fname in ("forward", "forward_delta"):
+            setattr(lin, fname, timed(kind, getattr(lin, fname),
+                                      lambda r, x, *a, **k: (2.0 * x.shape[0] * w, 2 * w + nbytes(x) + (nbytes(r) if r is not None else 4 * x.shape[0] * n_out))))
+
+    # attention: a pair of a query and a visible key costs, per head, the score and the weighted sum of every map
+    def attn_multi_work(r, q, store, batch, scale, **kw):
+        n, H, d = q.shape
+        e = kw["v_dim"]
+        return 2.0 * ctx["pairs"] * H * (d + kw["maps"] * e), nbytes(q, r) + ctx["kv_rows"] * store[0].numel() // 64 * store.element_size()
+
+    def attn_std_work(r, q, kv, batch, *a, **k):
+        n, H, d = q.shape
+        return 4.0 * ctx["pairs"] * H * d, nbytes(q, r) + ctx["kv_rows"] * kv[0].numel() // 64 * kv.element_size()
+
+    def rows_work(r, *a, **k):
+        ts = [t for t in a if torch.is_tensor(t)] + [t for t in k.values() if torch.is_tensor(t) and t.dim() >= 2 and t.numel() < (1 << 26)]
+        out = [t for t in (r if isinstance(r, tuple) else (r,)) if torch.is_tensor(t)]
+        return 0.0, nbytes(*[t for t in ts if t.numel() < (1 << 26)], *out)
+
+    def absorb_work(r, parts, uk, H, d, dr, rank, **k):
+        return 2.0 * parts.shape[1] * H * d * rank, nbytes(parts, uk, r)
+
+    def expand_work(r, y, uv, gate, H, e, rank, **k):
+        return 2.0 * y.shape[0] * H * e * rank, nbytes(y, uv, r)
+
+    def norm_work(r, x, delta=None, *a, **k):
+        return 0.0, nbytes(x, delta) + (nbytes(x) if delta is not None and k.get("rows") is None else 0) + (nbytes(r) if r is not None and r is not x else 0)
+
+    for fname, kind, work in (("attention_multi", "attention", attn_multi_work), ("attention_prompt", "attention", attn_std_work),
+                              ("attention_decode", "attention", attn_std_work), ("qkv_finish", "finish", rows_work),
+                              ("latent_finish", "finish", rows_work), ("qk_norm_rope_append", "finish", rows_work),
+                              ("latent_absorb", "query into the rows' space", absorb_work),
+                              ("latent_expand", "values out of the rows' space", expand_work), ("stream_update", "norm", norm_work),
+                              ("rmsnorm", "norm", lambda r, x, *a, **k: norm_work(r, x, k.get("delta"), rows=k.get("rows"))),
+                              ("gelu_gate_rows", "side input", rows_work)):
+        setattr(ops, fname, timed(kind, getattr(ops, fname), work))       # (the parts call these through the module)
+    # (the fused decode attention of the standard mixer would hide its parts: the plain sequence of kernels is timed instead)
+    ops.attention_decode_parts_supported = lambda *a, **k: False
+    for blk in eng.model.blocks:
+        m = blk.mixer
+        for attr, kind in (("qkv", "projections into the mixer"), ("down", "projections into the mixer"),
+                           ("uq", "projections into the mixer"), ("o", "o product")):
+            if isinstance(getattr(m, attr, None), Linear):
+                product(kind, getattr(m, attr))
+        for attr in ("gate_up", "down"):
+            product("feed-forward", getattr(blk.ffn, attr))
+        if blk.side is not None:
+            product("side input", blk.side.gate)
+            product("side input", blk.side.proj)
+
+    def collect():
+        torch.cuda.synchronize()
+        res = {}
+        for kind, evs in acc.items():
+            us = sum(e[0].elapsed_time(e[1]) for e in evs) * 1e3
+            fl, by = sum(e[2] for e in evs), sum(e[3] for e in evs)
+            r = res[kind] = {"us_per_step": us, "calls": len(evs)}
+            if fl:
+                r["tflops"] = fl / (us * 1e-6) / 1e12
+                r["tflops_frac"] = r["tflops"] / pk["bf16_tflops"]
+            r["gbs"] = by / (us * 1e-6) / 1e9
+            r["gbs_frac"] = r["gbs"] / pk["hbm_gbs"]
+        acc.clear()
+        return res
+
+    out = {}
+    win, keep = (z["window"], z["keep_first"]) if name == "tuguvik" else (None, 0)
+    seen = lambda p: p + 1 if win is None else min(p + 1, win + (keep if name == "tuguvik" else 0))   # (an upper bound for kept keys)
+    ptoks = random_prompts(torch, z["vocab"], [PREFILL], 3)[0]
+    ctx["pairs"], ctx["kv_rows"] = sum(seen(p) for p in range(PREFILL)), PREFILL
+    for i in range(3):
+        s = eng.open_seq()
+        acc.clear()
+        eng.step([s], [ptoks])
+        eng.close_seq(s)
+    out["prompt_2048"] = collect()
+    slots = [eng.open_seq() for _ in range(8)]
+    eng.step(slots, random_prompts(torch, z["vocab"], [1500] * 8, 4))
+    ctx["pairs"] = ctx["kv_rows"] = 8 * seen(1503)
+    for i in range(4):
+        acc.clear()
+        eng.step(slots, [[1 + i]] * 8)
+    out["decode_b8_ctx1500"] = collect()
+    return out
+
+
+def tuguvik_compare(args) -> int:
+    import torch
+    import wick_b200 as wick
+    pk = peaks()
+    z = TUGUVIK_SIZES[args.design_size]
+    cfgs = tuguvik_configs(z)
+    if args.design_parts:
+        print(json.dumps({args.design_parts: tuguvik_parts(torch, wick, pk, z, args.design_parts, cfgs[args.design_parts])}))
+        return 0
+    steps, warmup = min(args.steps, 64), max(args.warmup, 3)
+    with Clocks() as clk:
+        models = {name: design_model(torch, wick, pk, z, name, cfgs[name], steps, warmup) for name in ("tuguvik", "qwen3")}
+    env = dict(os.environ, WICK_B200_NO_PDL="1")
+    parts, errors = {}, {}
+    for name in ("tuguvik", "qwen3"):                  # (a process each: the timing wrappers replace the module's functions)
+        r = subprocess.run([sys.executable, os.path.abspath(__file__), "--design", "tuguvik", "--design-size", args.design_size,
+                            "--design-parts", name], env=env, capture_output=True, text=True)
+        for ln in r.stdout.splitlines():
+            if ln.startswith("{"):
+                parts.update(json.loads(ln))
+        if name not in parts:
+            errors[name] = r.stderr[-600:]
+    line = {"metric": f"Tuguvik beside Qwen3 at equal size ({args.design_size}): prefill and decode tok/s, bf16", "unit": "tokens/s",
+            "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16", "sizes": z,
+            "data": "synthetic: seeded random weights, seeded uniform random token ids", "models": models, "parts": parts,
+            "parts_error": errors or None, "clocks": clk.result, "peaks": pk}
+    print(json.dumps(line))
+    return 0 if all(m["finite"] for m in models.values()) else 1
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -431,12 +616,15 @@ def main() -> int:
     ap.add_argument("--skip-prefill", action="store_true")
     ap.add_argument("--skip-decode", action="store_true", help="prefill only (for profiling)")
     ap.add_argument("--eager", action="store_true", help="no CUDA graphs (every kernel is a launch of its own)")
-    ap.add_argument("--design", default=None, choices=["nibotar"], help="another line: this design beside Qwen3 at equal size")
+    ap.add_argument("--design", default=None, choices=["nibotar", "tuguvik"], help="another line: this design beside Qwen3 at equal size")
     ap.add_argument("--design-size", default="2k", choices=sorted(DESIGN_SIZES))
-    ap.add_argument("--design-parts", action="store_true", help="only the per-kernel times of --design (run by --design itself)")
+    ap.add_argument("--design-parts", nargs="?", const="both", default=None,
+                    help="only the per-kernel times of --design (run by --design itself; tuguvik: of the model named)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
+    if args.design == "tuguvik":
+        return tuguvik_compare(args)
     if args.design:
         return design_compare(args)
     if args.gpus != 1:
