@@ -299,6 +299,42 @@ def test_one_map_over_cached_rows_with_a_sink(dtype, H, r, dr, window):
         close(out, ref[start:start + n], name, f"{n} tokens after {start}", 3e-5)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_long_rows_of_keys_are_cut_into_runs_and_merged(dtype):
+    """A step of few tokens over many keys: the keys go through several blocks whose records are merged (with the sink,
+    with the two maps' combination), and heads that read the same rows share a block (groups of 4, 2 and 1 heads)."""
+    g = torch.Generator().manual_seed(8)
+    m = 1300
+    name = "float32" if dtype == torch.float32 else "bfloat16"
+    pages = list(range(21, 0, -1))
+    for H, r, dr, window in ((8, 40, 8, 0), (6, 136, 8, 1100), (3, 24, 16, 0)):
+        R = r + dr
+        q = torch.randn(m, H, R, generator=g)
+        rows = torch.randn(m, R, generator=g).to(dtype)
+        sink = torch.randn(H, generator=g)
+        store = torch.full((23, PAGE, R), float("nan"), dtype=dtype)
+        for j in range(m):
+            store[pages[j // PAGE], j % PAGE] = rows[j]
+        s = torch.einsum("ihd,jd->hij", q.double(), rows.double()) * 0.1
+        ref = torch.einsum("hij,je->ihe", P.softmax_visible(s, P.window_visible(m, window or None), sink.double()), rows.double()[:, :r])
+        for start, n in ((1299, 1), (1024, 2), (600, 1), (5, 1)):
+            b = seq_batch(n, start, pages[:(start + n + PAGE - 1) // PAGE])
+            out = ops.attention_multi(q[start:start + n].to(DEV), store.to(DEV), b, 0.1, maps=1, kv_heads=1, v_dim=r, window=window,
+                                      sink=sink.to(DEV), rows_of=R, out_dtype=torch.float32)
+            close(out, ref[start:start + n], name, f"rows: {n} tokens after {start}, {H} heads", 3e-5)
+    H, G, dm, e, window, keep = 4, 2, 16, 24, 900, 40
+    q = torch.randn(m, H, 2, dm, generator=g).to(dtype)
+    k = torch.randn(m, G, 2, dm, generator=g).to(dtype)
+    v = torch.randn(m, G, e, generator=g).to(dtype)
+    kv = fill_pages(k.reshape(m, G, 2 * dm), v, pages, 23, dtype).to(DEV)
+    ref = plain_two_maps(q.double(), k.double(), v.double(), 0.2, window, keep, 0.45, 1e-5, 0.65)
+    for start, n in ((1299, 1), (939, 2), (600, 1)):
+        b = seq_batch(n, start, pages[:(start + n + PAGE - 1) // PAGE])
+        out = ops.attention_multi(q[start:start + n].reshape(n, H, 2 * dm).to(DEV), kv, b, 0.2, maps=2, kv_heads=G, v_dim=e, window=window,
+                                  keep_first=keep, combine=(0.45, 1e-5, 0.65), out_dtype=dtype)
+        close(out, ref[start:start + n], name, f"two maps: {n} tokens after {start}", 3e-5 if dtype == torch.float32 else 3e-2)
+
+
 def test_the_sink_takes_its_share_and_a_row_outside_the_window_none():
     """One visible row with score 0 and a sink s: the row's weight is 1 / (1 + exp(s)).  A row that dominates is seen
     from positions j .. j + window - 1 and from no other."""

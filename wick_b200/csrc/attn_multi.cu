@@ -1,7 +1,7 @@
 // Attention whose heads hold more than one score map, over paged storage described by
 // strides, and the kernels around attention through a cached latent.
 //
-//   attend   : every new token over the cache.  A query head holds MAPS vectors of dm numbers;
+//   attend   : every new token over the cache (for steps of few tokens: the keys in runs over several blocks, then a merge).  A query head holds MAPS vectors of dm numbers;
 //              map a scores the a-th dm numbers of the key row, has a softmax of its own, and
 //              weighs the SAME value rows.  Visible keys of the query at position p: with a
 //              window, the keys j <= p with p - j < window or j < keep_first; else every j <= p.
@@ -37,157 +37,17 @@ __device__ __forceinline__ void mv_load4(const __nv_bfloat16* p, float* v) {
 // The v-th visible key (v counts the kept first keys, then the window).
 __device__ __forceinline__ int visible_key(int v, int n_kept, int lo) { return v < n_kept ? v : lo + (v - n_kept); }
 
-// One block per (token, query head); its warps share the visible keys, 32 at a time.  In a tile,
-// lane l scores key l of the tile for every map (dot products in index order), the running maximum
-// and sum of each map follow, then every lane adds the tile's weighted value rows into its own
-// elements of each map's result.  The warps' partial results are folded in warp order by warp 0.
-template <typename T, typename TQ, typename TO, int MAPS>
-__global__ void __launch_bounds__(256)
-attn_multi_kernel(const TQ* __restrict__ q, const T* __restrict__ store, TO* __restrict__ out,
-                  const int* __restrict__ seq_of_token, const int* __restrict__ positions,
-                  const int* __restrict__ page_table, int table_width, int H, int G, int dm, int e, int64_t page_elems,
-                  int k_row, int64_t v_off, int v_row, float scale, int window, int keep_first,
-                  const float* __restrict__ sink, float lam, float eps, float factor) {
-    extern __shared__ float smem[];
-    pdl_trigger();
-    pdl_wait();
-    q = fresh(q);
-    store = fresh(store);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
-    const int t = blockIdx.x / H, h = blockIdx.x - t * H;
-    const int g = h / (H / G);
-    const int pos = positions[t];
-    const int* table = page_table + (int64_t)seq_of_token[t] * table_width;
-    const int d = MAPS * dm, d_pad = (d + 3) & ~3, e_pad = (e + 127) / 128 * 128;
-    float* qs = smem;                           // [d]
-    float* ms = qs + d_pad;                     // [warps][MAPS] maxima, then [warps][MAPS] sums
-    float* accs = ms + 2 * MAPS * n_warps;      // [warps][MAPS][e_pad]
-    for (int x = threadIdx.x; x < d; x += blockDim.x) qs[x] = ld(q + ((int64_t)t * H + h) * d + x);
-    __syncthreads();
-    constexpr int VN = Vec16<T>::N;
-    const bool base_ok = (((uintptr_t)store) & 15) == 0;
-    const bool k_vec = base_ok && dm % VN == 0 && k_row % VN == 0 && page_elems % VN == 0;
-    const bool v_vec = base_ok && e % 4 == 0 && v_row % 4 == 0 && page_elems % 4 == 0 && v_off % 4 == 0;
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int n_kept = window > 0 ? min(keep_first, lo) : 0;
-    const int total = n_kept + (pos - lo + 1);
-    float m[MAPS], l[MAPS], acc[MAPS][4 * MV_CHUNKS];
-#pragma unroll
-    for (int a = 0; a < MAPS; ++a) {
-        m[a] = -INFINITY;
-        l[a] = 0.f;
-#pragma unroll
-        for (int c = 0; c < 4 * MV_CHUNKS; ++c) acc[a][c] = 0.f;
-    }
-    for (int v0 = 32 * warp; v0 < total; v0 += 32 * n_warps) {
-        const int vi = v0 + lane;
-        const bool valid = vi < total;
-        float s[MAPS], p[MAPS];
-#pragma unroll
-        for (int a = 0; a < MAPS; ++a) s[a] = -INFINITY;
-        if (valid) {
-            const int key = visible_key(vi, n_kept, lo);
-            const T* kp = store + (int64_t)table[key / kPage] * page_elems + ((int64_t)g * kPage + (key % kPage)) * k_row;
-#pragma unroll
-            for (int a = 0; a < MAPS; ++a) {
-                const float* qa = qs + a * dm;
-                const T* ka = kp + a * dm;
-                float dot = 0.f;
-                if (k_vec) {
-                    for (int x = 0; x < dm; x += 2 * VN) {           // two loads of 16 bytes in flight
-                        Vec16<T> kk[2];
-                        kk[0].load(ka + x);
-                        if (x + VN < dm) kk[1].load(ka + x + VN);
-#pragma unroll
-                        for (int i = 0; i < VN; ++i) dot = fmaf(qa[x + i], kk[0].v[i], dot);
-                        if (x + VN < dm) {
-#pragma unroll
-                            for (int i = 0; i < VN; ++i) dot = fmaf(qa[x + VN + i], kk[1].v[i], dot);
-                        }
-                    }
-                } else {
-                    for (int x = 0; x < dm; ++x) dot = fmaf(qa[x], ld(ka + x), dot);
-                }
-                s[a] = dot * scale;
-            }
-        }
-#pragma unroll
-        for (int a = 0; a < MAPS; ++a) {
-            const float m_new = fmaxf(m[a], warp_max(s[a]));         // finite: the tile's first key is visible
-            const float corr = expf(m[a] - m_new);                   // (m = -inf at first: 0)
-            p[a] = valid ? expf(s[a] - m_new) : 0.f;
-            l[a] = l[a] * corr + warp_sum(p[a]);
-            m[a] = m_new;
-#pragma unroll
-            for (int c = 0; c < 4 * MV_CHUNKS; ++c) acc[a][c] *= corr;
-        }
-        const int n_keys = min(32, total - v0);
-        for (int jj = 0; jj < n_keys; ++jj) {
-            const int key = visible_key(v0 + jj, n_kept, lo);
-            const T* vp = store + (int64_t)table[key / kPage] * page_elems + v_off + ((int64_t)g * kPage + (key % kPage)) * v_row;
-            float pj[MAPS];
-#pragma unroll
-            for (int a = 0; a < MAPS; ++a) pj[a] = __shfl_sync(0xffffffffu, p[a], jj);
-#pragma unroll
-            for (int c = 0; c < MV_CHUNKS; ++c) {
-                const int x = 128 * c + 4 * lane;
-                if (x < e) {
-                    float vv[4];
-                    if (v_vec) {
-                        mv_load4(vp + x, vv);
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) vv[i] = x + i < e ? ld(vp + x + i) : 0.f;
-                    }
-#pragma unroll
-                    for (int a = 0; a < MAPS; ++a)
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) acc[a][4 * c + i] = fmaf(pj[a], vv[i], acc[a][4 * c + i]);
-                }
-            }
-        }
-    }
-    if (lane == 0) {
-#pragma unroll
-        for (int a = 0; a < MAPS; ++a) {
-            ms[warp * MAPS + a] = m[a];
-            ms[(n_warps + warp) * MAPS + a] = l[a];
-        }
-    }
-#pragma unroll
-    for (int a = 0; a < MAPS; ++a)
-#pragma unroll
-        for (int c = 0; c < MV_CHUNKS; ++c)
-            if (128 * c < e_pad)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) accs[((int64_t)warp * MAPS + a) * e_pad + 128 * c + 4 * lane + i] = acc[a][4 * c + i];
-    __syncthreads();
-    if (warp != 0) return;
-    // warp 0 folds the warps' results, map by map; a lane holds its elements of the head's result
-    float y[MAPS][4 * MV_CHUNKS];
-#pragma unroll
-    for (int a = 0; a < MAPS; ++a) {
-        float big = sink ? sink[h] : -INFINITY;
-        for (int w = 0; w < n_warps; ++w) big = fmaxf(big, ms[w * MAPS + a]);      // finite: warp 0 holds a visible key
-        float sum = sink ? expf(sink[h] - big) : 0.f;
-#pragma unroll
-        for (int c = 0; c < 4 * MV_CHUNKS; ++c) y[a][c] = 0.f;
-        for (int w = 0; w < n_warps; ++w) {
-            const float mw = ms[w * MAPS + a];
-            const float f = mw == -INFINITY ? 0.f : expf(mw - big);
-            sum += ms[(n_warps + w) * MAPS + a] * f;
-#pragma unroll
-            for (int c = 0; c < MV_CHUNKS; ++c)
-                if (128 * c < e_pad)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        y[a][4 * c + i] = fmaf(accs[((int64_t)w * MAPS + a) * e_pad + 128 * c + 4 * lane + i], f, y[a][4 * c + i]);
-        }
-        const float inv = 1.0f / sum;
-#pragma unroll
-        for (int c = 0; c < 4 * MV_CHUNKS; ++c) y[a][c] *= inv;
-    }
-    TO* o = out + ((int64_t)t * H + h) * e;
+// One block per (token, GROUP query heads, run of the visible keys); its warps share the run's keys, 32 at a
+// time.  A block holds NQ = GROUP * MAPS query vectors of dm numbers ([head][map][dm], as they lie in memory); all
+// of them score the same key rows (map a the a-th dm numbers of a row) and weigh the same value rows, so a row is
+// read once for all of them.  In a tile, lane l scores key l of the tile for every vector (dot products in index
+// order), the running maximum and sum of each follow, then every lane adds the tile's weighted value rows into its
+// own elements of each vector's result.  The warps' partial results are folded in warp order, head gi by warp gi.
+// With `partial` the fold's result goes there as a record (maximum, sum, two unused numbers, unnormalised values) per (token, head,
+// map, run) for the merge kernel; without, the block holds all visible keys and finishes itself: the sink joins,
+// the sums are divided, MAPS = 2 is combined (y_1 - lambda y_2, then the norm over the head's values).
+template <int MAPS>
+__device__ __forceinline__ void finish_head(float (&y)[MAPS][4 * MV_CHUNKS], int lane, int e, float lam, float eps, float factor) {
     if (MAPS == 2) {
         float ss = 0.f;
 #pragma unroll
@@ -202,13 +62,188 @@ attn_multi_kernel(const TQ* __restrict__ q, const T* __restrict__ store, TO* __r
         ss = warp_sum(ss);
         const float f = 1.0f / sqrtf(ss / (float)e + eps);
 #pragma unroll
-        for (int c = 0; c < MV_CHUNKS; ++c)
+        for (int c = 0; c < 4 * MV_CHUNKS; ++c) y[0][c] = (y[0][c] * f) * factor;
+    }
+}
+
+template <typename T, typename TQ, typename TO, int MAPS, int GROUP>
+__global__ void __launch_bounds__(256)
+attn_multi_kernel(const TQ* __restrict__ q, const T* __restrict__ store, TO* __restrict__ out, float* __restrict__ partial,
+                  const int* __restrict__ seq_of_token, const int* __restrict__ positions,
+                  const int* __restrict__ page_table, int table_width, int H, int G, int dm, int e, int64_t page_elems,
+                  int k_row, int64_t v_off, int v_row, float scale, int window, int keep_first,
+                  const float* __restrict__ sink, float lam, float eps, float factor) {
+    constexpr int NQ = MAPS * GROUP;
+    extern __shared__ float smem[];
+    pdl_trigger();
+    pdl_wait();
+    q = fresh(q);
+    store = fresh(store);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int groups = H / GROUP;
+    const int t = blockIdx.x / groups, h0 = (blockIdx.x - t * groups) * GROUP;
+    const int g = h0 / (H / G);                  // (a group's heads share a key/value head: GROUP divides H / G)
+    const int pos = positions[t];
+    const int* table = page_table + (int64_t)seq_of_token[t] * table_width;
+    const int dq = NQ * dm, dq_pad = (dq + 3) & ~3, e_pad = (e + 127) / 128 * 128;
+    float* qs = smem;                           // [NQ][dm]
+    float* ms = qs + dq_pad;                    // [warps][NQ] maxima, then [warps][NQ] sums
+    float* accs = ms + 2 * NQ * n_warps;        // [warps][NQ][e_pad]
+    for (int x = threadIdx.x; x < dq; x += blockDim.x) qs[x] = ld(q + ((int64_t)t * H + h0) * (MAPS * dm) + x);
+    __syncthreads();
+    constexpr int VN = Vec16<T>::N;
+    const bool base_ok = (((uintptr_t)store) & 15) == 0;
+    const bool k_vec = base_ok && dm % VN == 0 && k_row % VN == 0 && page_elems % VN == 0;
+    const bool v_vec = base_ok && e % 4 == 0 && v_row % 4 == 0 && page_elems % 4 == 0 && v_off % 4 == 0;
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int n_kept = window > 0 ? min(keep_first, lo) : 0;
+    const int total = n_kept + (pos - lo + 1);
+    // this block's run of tiles
+    const int tiles = (total + 31) >> 5, per_run = (tiles + (int)gridDim.y - 1) / (int)gridDim.y;
+    const int v_begin = 32 * per_run * (int)blockIdx.y, v_end = min(total, 32 * per_run * ((int)blockIdx.y + 1));
+    float m[NQ], l[NQ], acc[NQ][4 * MV_CHUNKS];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int x = 128 * c + 4 * lane + i;
-                if (x < e) st(o + x, (y[0][4 * c + i] * f) * factor);
+    for (int a = 0; a < NQ; ++a) {
+        m[a] = -INFINITY;
+        l[a] = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4 * MV_CHUNKS; ++c) acc[a][c] = 0.f;
+    }
+    for (int v0 = v_begin + 32 * warp; v0 < v_end; v0 += 32 * n_warps) {
+        const int vi = v0 + lane;
+        const bool valid = vi < v_end;
+        float s[NQ], p[NQ];
+#pragma unroll
+        for (int a = 0; a < NQ; ++a) s[a] = 0.f;
+        if (valid) {
+            const int key = visible_key(vi, n_kept, lo);
+            const T* kp = store + (int64_t)table[key / kPage] * page_elems + ((int64_t)g * kPage + (key % kPage)) * k_row;
+#pragma unroll
+            for (int a = 0; a < MAPS; ++a) {
+                const T* ka = kp + a * dm;
+                if (k_vec) {
+                    for (int x = 0; x < dm; x += 2 * VN) {           // two loads of 16 bytes in flight
+                        Vec16<T> kk[2];
+                        kk[0].load(ka + x);
+                        const bool two = x + VN < dm;
+                        if (two) kk[1].load(ka + x + VN);
+#pragma unroll
+                        for (int gi = 0; gi < GROUP; ++gi) {
+                            const float* qa = qs + (gi * MAPS + a) * dm + x;
+                            float dot = s[gi * MAPS + a];
+#pragma unroll
+                            for (int i = 0; i < VN; ++i) dot = fmaf(qa[i], kk[0].v[i], dot);
+                            if (two) {
+#pragma unroll
+                                for (int i = 0; i < VN; ++i) dot = fmaf(qa[VN + i], kk[1].v[i], dot);
+                            }
+                            s[gi * MAPS + a] = dot;
+                        }
+                    }
+                } else {
+                    for (int x = 0; x < dm; ++x) {
+                        const float kx = ld(ka + x);
+#pragma unroll
+                        for (int gi = 0; gi < GROUP; ++gi) s[gi * MAPS + a] = fmaf(qs[(gi * MAPS + a) * dm + x], kx, s[gi * MAPS + a]);
+                    }
+                }
             }
-    } else {
+        }
+#pragma unroll
+        for (int a = 0; a < NQ; ++a) {
+            s[a] = valid ? s[a] * scale : -INFINITY;
+            const float m_new = fmaxf(m[a], warp_max(s[a]));         // finite: the tile's first key is visible
+            const float corr = expf(m[a] - m_new);                   // (m = -inf at first: 0)
+            p[a] = valid ? expf(s[a] - m_new) : 0.f;
+            l[a] = l[a] * corr + warp_sum(p[a]);
+            m[a] = m_new;
+#pragma unroll
+            for (int c = 0; c < 4 * MV_CHUNKS; ++c) acc[a][c] *= corr;
+        }
+        const int n_keys = min(32, v_end - v0);
+        for (int jj = 0; jj < n_keys; ++jj) {
+            const int key = visible_key(v0 + jj, n_kept, lo);
+            const T* vp = store + (int64_t)table[key / kPage] * page_elems + v_off + ((int64_t)g * kPage + (key % kPage)) * v_row;
+            float pj[NQ];
+#pragma unroll
+            for (int a = 0; a < NQ; ++a) pj[a] = __shfl_sync(0xffffffffu, p[a], jj);
+#pragma unroll
+            for (int c = 0; c < MV_CHUNKS; ++c) {
+                const int x = 128 * c + 4 * lane;
+                if (x < e) {
+                    float vv[4];
+                    if (v_vec) {
+                        mv_load4(vp + x, vv);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) vv[i] = x + i < e ? ld(vp + x + i) : 0.f;
+                    }
+#pragma unroll
+                    for (int a = 0; a < NQ; ++a)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) acc[a][4 * c + i] = fmaf(pj[a], vv[i], acc[a][4 * c + i]);
+                }
+            }
+        }
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int a = 0; a < NQ; ++a) {
+            ms[warp * NQ + a] = m[a];
+            ms[(n_warps + warp) * NQ + a] = l[a];
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < NQ; ++a)
+#pragma unroll
+        for (int c = 0; c < MV_CHUNKS; ++c)
+            if (128 * c < e_pad)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) accs[((int64_t)warp * NQ + a) * e_pad + 128 * c + 4 * lane + i] = acc[a][4 * c + i];
+    __syncthreads();
+    // warp gi folds head gi's maps over the block's warps; a lane holds its elements of the head's result
+    for (int gi = warp; gi < GROUP; gi += n_warps) {
+        const int h = h0 + gi;
+        float y[MAPS][4 * MV_CHUNKS];
+#pragma unroll
+        for (int a = 0; a < MAPS; ++a) {
+            const int qa = gi * MAPS + a;
+            const bool with_sink = sink && !partial;
+            float big = with_sink ? sink[h] : -INFINITY;
+            for (int w = 0; w < n_warps; ++w) big = fmaxf(big, ms[w * NQ + qa]);
+            float sum = with_sink ? expf(sink[h] - big) : 0.f;
+#pragma unroll
+            for (int c = 0; c < 4 * MV_CHUNKS; ++c) y[a][c] = 0.f;
+            for (int w = 0; w < n_warps; ++w) {
+                const float mw = ms[w * NQ + qa];
+                const float f = mw == -INFINITY ? 0.f : expf(mw - big);
+                sum += ms[(n_warps + w) * NQ + qa] * f;
+#pragma unroll
+                for (int c = 0; c < MV_CHUNKS; ++c)
+                    if (128 * c < e_pad)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            y[a][4 * c + i] = fmaf(accs[((int64_t)w * NQ + qa) * e_pad + 128 * c + 4 * lane + i], f, y[a][4 * c + i]);
+            }
+            if (partial) {                       // a record: maximum, sum, then the unnormalised values
+                float* rec = partial + ((((int64_t)t * H + h) * MAPS + a) * gridDim.y + blockIdx.y) * (4 + e_pad);
+                if (lane == 0) {
+                    rec[0] = big;
+                    rec[1] = sum;
+                }
+#pragma unroll
+                for (int c = 0; c < MV_CHUNKS; ++c)
+                    if (128 * c < e_pad) *reinterpret_cast<float4*>(rec + 4 + 128 * c + 4 * lane) =
+                        make_float4(y[a][4 * c], y[a][4 * c + 1], y[a][4 * c + 2], y[a][4 * c + 3]);
+            } else {
+                const float inv = 1.0f / sum;    // (the block holds a visible key: the sum is positive)
+#pragma unroll
+                for (int c = 0; c < 4 * MV_CHUNKS; ++c) y[a][c] *= inv;
+            }
+        }
+        if (partial) continue;
+        finish_head<MAPS>(y, lane, e, lam, eps, factor);
+        TO* o = out + ((int64_t)t * H + h) * e;
 #pragma unroll
         for (int c = 0; c < MV_CHUNKS; ++c)
 #pragma unroll
@@ -217,6 +252,59 @@ attn_multi_kernel(const TQ* __restrict__ q, const T* __restrict__ store, TO* __r
                 if (x < e) st(o + x, y[0][4 * c + i]);
             }
     }
+}
+
+// One warp per (token, head): the records of the runs of keys (a run that held no key has the maximum -inf) are
+// folded in run order, map by map; the sink joins; the sums are divided; two maps are combined.
+template <typename TO, int MAPS>
+__global__ void __launch_bounds__(128)
+attn_multi_merge_kernel(const float* __restrict__ partial, TO* __restrict__ out, int n_heads_total, int H, int e, int runs,
+                        const float* __restrict__ sink, float lam, float eps, float factor) {
+    pdl_trigger();
+    pdl_wait();
+    partial = fresh(partial);
+    const int lane = threadIdx.x & 31;
+    const int th = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);      // token * H + head
+    if (th >= n_heads_total) return;
+    const int h = th % H, e_pad = (e + 127) / 128 * 128;
+    float y[MAPS][4 * MV_CHUNKS];
+#pragma unroll
+    for (int a = 0; a < MAPS; ++a) {
+        const float* recs = partial + ((int64_t)th * MAPS + a) * runs * (4 + e_pad);
+        float big = sink ? sink[h] : -INFINITY;
+        for (int r = 0; r < runs; ++r) big = fmaxf(big, recs[(int64_t)r * (4 + e_pad)]);
+        float sum = sink ? expf(sink[h] - big) : 0.f;
+#pragma unroll
+        for (int c = 0; c < 4 * MV_CHUNKS; ++c) y[a][c] = 0.f;
+        for (int r = 0; r < runs; ++r) {
+            const float* rec = recs + (int64_t)r * (4 + e_pad);
+            const float mr = rec[0];
+            if (mr == -INFINITY) continue;
+            const float f = expf(mr - big);
+            sum += rec[1] * f;
+#pragma unroll
+            for (int c = 0; c < MV_CHUNKS; ++c)
+                if (128 * c < e_pad) {
+                    const float4 v = *reinterpret_cast<const float4*>(rec + 4 + 128 * c + 4 * lane);
+                    y[a][4 * c] = fmaf(v.x, f, y[a][4 * c]);
+                    y[a][4 * c + 1] = fmaf(v.y, f, y[a][4 * c + 1]);
+                    y[a][4 * c + 2] = fmaf(v.z, f, y[a][4 * c + 2]);
+                    y[a][4 * c + 3] = fmaf(v.w, f, y[a][4 * c + 3]);
+                }
+        }
+        const float inv = 1.0f / sum;
+#pragma unroll
+        for (int c = 0; c < 4 * MV_CHUNKS; ++c) y[a][c] *= inv;
+    }
+    finish_head<MAPS>(y, lane, e, lam, eps, factor);
+    TO* o = out + (int64_t)th * e;
+#pragma unroll
+    for (int c = 0; c < MV_CHUNKS; ++c)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int x = 128 * c + 4 * lane + i;
+            if (x < e) st(o + x, y[0][4 * c + i]);
+        }
 }
 
 // ---------------------------------------------------------------------------
@@ -311,7 +399,7 @@ latent_absorb_kernel(const float* __restrict__ parts, int splits, int64_t split_
     for (int idx = tid + n_t * dq; idx < LAT_TT * dq; idx += blockDim.x) qh[idx] = 0.f;
     __syncthreads();
     const int half = dr >> 1;
-    for (int idx = tid; idx < n_t * half; idx += blockDim.x) {
+    for (int idx = tid; idx < (blockIdx.z == 0 ? n_t * half : 0); idx += blockDim.x) {
         const int tt = idx / half, i = idx - tt * half;
         const int j0 = pairing == 0 ? 2 * i : i, j1 = pairing == 0 ? 2 * i + 1 : i + half;
         float u = qh[tt * dq + d + j0], v = qh[tt * dq + d + j1];
@@ -325,9 +413,9 @@ latent_absorb_kernel(const float* __restrict__ parts, int splits, int64_t split_
         o[j0] = u;
         o[j1] = v;
     }
-    if ((dr & 1) && tid < n_t) out[((int64_t)(t0 + tid) * H + h) * (r + dr) + r + dr - 1] = qh[tid * dq + d + dr - 1];
+    if ((dr & 1) && tid < n_t && blockIdx.z == 0) out[((int64_t)(t0 + tid) * H + h) * (r + dr) + r + dr - 1] = qh[tid * dq + d + dr - 1];
     const T* w = uk + (int64_t)h * d * r;
-    for (int j = tid; j < r; j += blockDim.x) {
+    for (int j = blockIdx.z * blockDim.x + tid; j < r; j += gridDim.z * blockDim.x) {      // (the blocks along z share the columns)
         float acc[LAT_TT];
 #pragma unroll
         for (int tt = 0; tt < LAT_TT; ++tt) acc[tt] = 0.f;
@@ -361,7 +449,7 @@ latent_expand_kernel(const float* __restrict__ y, const T* __restrict__ uv, cons
         ys[idx] = tt < n_t ? y[((int64_t)(t0 + tt) * H + h) * r + j] : 0.f;
     }
     __syncthreads();
-    for (int x = warp; x < e; x += n_warps) {
+    for (int x = blockIdx.z * n_warps + warp; x < e; x += gridDim.z * n_warps) {             // (the blocks along z share the rows)
         const T* w = uv + ((int64_t)h * e + x) * r;
         float acc[LAT_TT];
 #pragma unroll
@@ -385,25 +473,56 @@ latent_expand_kernel(const float* __restrict__ y, const T* __restrict__ uv, cons
 }
 
 // ---------------------------------------------------------------------------
+template <typename T, typename TQ, typename TO, int MAPS, int GROUP>
+int attn_multi_launch(const void* q, const void* store, void* out, float* partial, const int* seq_of_token, const int* positions,
+                      const int* page_table, int table_width, int n, int H, int G, int dm, int e, int64_t page_elems, int k_row,
+                      int64_t v_off, int v_row, float scale, int window, int keep_first, const float* sink, float lam, float eps,
+                      float factor, int warps, int runs, cudaStream_t s) {
+    constexpr int NQ = MAPS * GROUP;
+    const int dq_pad = (NQ * dm + 3) & ~3, e_pad = (e + 127) / 128 * 128;
+    const size_t smem = ((size_t)dq_pad + 2 * NQ * warps + (size_t)warps * NQ * e_pad) * sizeof(float);
+    WICK_REQUIRE(smem <= 160 * 1024, "attn_multi: heads of %d numbers are beyond one block's shared memory", NQ * dm);
+    static size_t raised = 48 * 1024;
+    if (smem > raised) {
+        WICK_CUDA(cudaFuncSetAttribute(attn_multi_kernel<T, TQ, TO, MAPS, GROUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        raised = 160 * 1024;
+    }
+    WICK_CUDA(launch(attn_multi_kernel<T, TQ, TO, MAPS, GROUP>, dim3((unsigned)(n * (H / GROUP)), runs), dim3(32 * warps), smem, s,
+                     (const TQ*)q, (const T*)store, (TO*)out, partial, seq_of_token, positions, page_table, table_width, H, G, dm, e,
+                     page_elems, k_row, v_off, v_row, scale, window, keep_first, sink, lam, eps, factor));
+    if (int rc = check_launch("attn_multi")) return rc;
+    if (partial) {
+        WICK_CUDA(launch(attn_multi_merge_kernel<TO, MAPS>, dim3(ceil_div((int64_t)n * H, 4)), dim3(128), 0, s, (const float*)partial,
+                         (TO*)out, n * H, H, e, runs, sink, lam, eps, factor));
+        return check_launch("attn_multi_merge");
+    }
+    return 0;
+}
+
+// few: the step has few tokens (one per sequence): eight warps share a block's keys, heads that read the same rows go
+// through a block together (up to four), and the visible keys are cut into `runs` runs, a block each, whose records
+// (`partial`: n * H * MAPS * runs * (4 + e rounded up to 128) floats, 16-byte aligned) a second kernel merges.
 template <typename T, typename TQ, typename TO, int MAPS>
-int attn_multi(const void* q, const void* store, void* out, const int* seq_of_token, const int* positions,
+int attn_multi(const void* q, const void* store, void* out, float* partial, const int* seq_of_token, const int* positions,
                const int* page_table, int table_width, int n, int H, int G, int dm, int e, int64_t page_elems, int k_row,
                int64_t v_off, int v_row, float scale, int window, int keep_first, const float* sink, float lam, float eps,
-               float factor, int few, cudaStream_t s) {
+               float factor, int few, int runs, cudaStream_t s) {
     WICK_REQUIRE(H > 0 && G > 0 && H % G == 0 && dm > 0 && e > 0, "attn_multi: bad head counts or sizes");
     WICK_REQUIRE(e <= 128 * MV_CHUNKS, "attn_multi: a value size of %d is beyond %d", e, 128 * MV_CHUNKS);
     WICK_REQUIRE(window >= 0 && keep_first >= 0, "attn_multi: bad window");
-    if (n == 0) return 0;
-    // warps that share a token's keys: several where the step has few tokens, one where it has many
-    const int warps = few ? 4 : 1;
-    const int d_pad = (MAPS * dm + 3) & ~3, e_pad = (e + 127) / 128 * 128;
-    const size_t smem = ((size_t)d_pad + 2 * MAPS * warps + (size_t)warps * MAPS * e_pad) * sizeof(float);
-    WICK_REQUIRE(smem <= 48 * 1024, "attn_multi: a head of %d numbers is beyond one block's shared memory", MAPS * dm);
+    WICK_REQUIRE(runs >= 1 && runs <= 64 && (runs == 1 || partial), "attn_multi: %d runs of keys need a place for their records", runs);
     WICK_REQUIRE((int64_t)n * H <= 0x7fffffff, "attn_multi: too many (token, head) pairs");
-    WICK_CUDA(launch(attn_multi_kernel<T, TQ, TO, MAPS>, dim3((unsigned)(n * H)), dim3(32 * warps), smem, s, (const TQ*)q, (const T*)store,
-                     (TO*)out, seq_of_token, positions, page_table, table_width, H, G, dm, e, page_elems, k_row, v_off, v_row, scale,
-                     window, keep_first, sink, lam, eps, factor));
-    return check_launch("attn_multi");
+    if (n == 0) return 0;
+    if (runs == 1) partial = nullptr;
+    const int warps = few ? 8 : 1, per_kv = H / G;
+#define WICK_AM(GROUP)                                                                                                          \
+    return attn_multi_launch<T, TQ, TO, MAPS, GROUP>(q, store, out, partial, seq_of_token, positions, page_table, table_width, n, H, G, \
+                                                     dm, e, page_elems, k_row, v_off, v_row, scale, window, keep_first, sink, lam,   \
+                                                     eps, factor, warps, runs, s)
+    if (MAPS == 1 && few && per_kv % 4 == 0) WICK_AM(4);
+    if (MAPS == 1 && few && per_kv % 2 == 0) WICK_AM(2);
+    WICK_AM(1);
+#undef WICK_AM
 }
 
 template <typename T>
@@ -430,7 +549,7 @@ int latent_absorb(const float* parts, int splits, const void* uk, int n, int H, 
     if (n == 0) return 0;
     const size_t smem = (size_t)LAT_TT * (d + dr) * sizeof(float);
     WICK_REQUIRE(smem <= 48 * 1024, "latent_absorb: a head of %d numbers is beyond one block's shared memory", d + dr);
-    WICK_CUDA(launch(latent_absorb_kernel<T>, dim3(ceil_div(n, LAT_TT), H), dim3(256), smem, s, parts, splits,
+    WICK_CUDA(launch(latent_absorb_kernel<T>, dim3(ceil_div(n, LAT_TT), H, min(64, ceil_div(r, 128))), dim3(128), smem, s, parts, splits,
                      (int64_t)n * H * (d + dr), (const T*)uk, n, H, d, dr, r, cos_t, sin_t, pairing, out));
     return check_launch("latent_absorb");
 }
@@ -441,7 +560,8 @@ int latent_expand(const float* y, const void* uv, const float* gate, int n, int 
     if (n == 0) return 0;
     const size_t smem = (size_t)LAT_TT * r * sizeof(float);
     WICK_REQUIRE(smem <= 48 * 1024, "latent_expand: a latent of %d numbers is beyond one block's shared memory", r);
-    WICK_CUDA(launch(latent_expand_kernel<T>, dim3(ceil_div(n, LAT_TT), H), dim3(256), smem, s, y, (const T*)uv, gate, n, H, e, r, (T*)out));
+    WICK_CUDA(launch(latent_expand_kernel<T>, dim3(ceil_div(n, LAT_TT), H, min(64, ceil_div(e, 32))), dim3(256), smem, s, y, (const T*)uv, gate,
+                     n, H, e, r, (T*)out));
     return check_launch("latent_expand");
 }
 
@@ -457,10 +577,10 @@ typedef __nv_bfloat16 bf16;
     WICK_API int NAME(const void* q, const void* store, void* out, const int* seq_of_token, const int* positions,               \
                       const int* page_table, int table_width, int n, int H, int G, int dm, int e, int64_t page_elems, int k_row, \
                       int64_t v_off, int v_row, float scale, int window, int keep_first, const float* sink, float lam, float eps, \
-                      float factor, int few, void* s) {                                                                          \
-        return attn_multi<T, TQ, TO, MAPS>(q, store, out, seq_of_token, positions, page_table, table_width, n, H, G, dm, e,      \
-                                           page_elems, k_row, v_off, v_row, scale, window, keep_first, sink, lam, eps, factor,   \
-                                           few, (cudaStream_t)s);                                                                \
+                      float factor, int few, int runs, float* partial, void* s) {                                                \
+        return attn_multi<T, TQ, TO, MAPS>(q, store, out, partial, seq_of_token, positions, page_table, table_width, n, H, G, dm, \
+                                           e, page_elems, k_row, v_off, v_row, scale, window, keep_first, sink, lam, eps,        \
+                                           factor, few, runs, (cudaStream_t)s);                                                  \
     }
 WICK_ATTN_MULTI(wick_attn_multi2_bf16, bf16, bf16, bf16, 2)
 WICK_ATTN_MULTI(wick_attn_multi2_f32, float, float, float, 2)

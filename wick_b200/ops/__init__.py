@@ -691,10 +691,26 @@ def attention_multi(q: torch.Tensor, store: torch.Tensor, batch, scale: float, *
         name = f"wick_attn_multi1_{'bf16' if T == torch.bfloat16 else 'f32'}"
         lam, eps, factor = 0.0, 0.0, 1.0
     out = torch.empty((n, H, v_dim), dtype=out_dtype, device=q.device)
-    few = 1 if n * H < 4 * 148 else 0
-    _layer().call(name, "ppppppiiiiiililifiipfffip", _p(q), _p(store), _p(out), _p(batch.seq_of_token), _p(batch.positions),
+    # A step of few tokens: eight warps a block, heads that read the same rows together, and the visible keys cut into
+    # runs (a block each, records merged by a second kernel) until the step fills the device about twice.  How many keys
+    # a token can see at most is known from the window or from the step's bound on cached positions.
+    few = 1 if n * H <= 8 * 148 else 0
+    runs, partial = 1, None
+    if few:
+        group = 1 if maps == 2 else (4 if (H // kv_heads) % 4 == 0 else (2 if (H // kv_heads) % 2 == 0 else 1))
+        bound = getattr(batch, "kv_bound", None) or batch.max_kv_len
+        keys = min(bound, window + keep_first) if window > 0 else bound
+        tiles = (max(1, keys) + 31) // 32
+        runs = max(1, min(-(-2 * 148 // (n * (H // group))), tiles // 8, 16))
+        if runs > 1:
+            need = n * H * maps * runs * (4 + (v_dim + 127) // 128 * 128)
+            ws = getattr(batch, "workspace", None)
+            partial = ws.get("attention_multi", need, torch.float32) if ws is not None else \
+                torch.empty(need, dtype=torch.float32, device=q.device)
+    _layer().call(name, "ppppppiiiiiililifiipfffiipp", _p(q), _p(store), _p(out), _p(batch.seq_of_token), _p(batch.positions),
                   _p(batch.page_table), batch.table_width, n, H, kv_heads, dm, v_dim, page_elems, k_row, v_off, v_row, float(scale),
-                  int(window), int(keep_first), _p(sink), float(lam), float(eps), float(factor), few, _stream())
+                  int(window), int(keep_first), _p(sink), float(lam), float(eps), float(factor), few, runs, _p(partial), _stream(),
+                  kernels=2 if partial is not None else 1)
     return out
 
 
