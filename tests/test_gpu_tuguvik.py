@@ -444,6 +444,153 @@ def test_the_kernels_around_the_latent(dtype, H, d, dr, e, qr, r, own):
     close(out.reshape(n, H, e), ref, name, "values of the heads", tol)
 
 
+def flex_two_maps(q, kv, batch, scale, H, G, dm, e, window, keep, combine):
+    """The tensor-core form of two maps over the paged keys and values: every map of every head a head of its own."""
+    n, d = q.shape[0], 2 * dm
+    page, per = G * PAGE * (d + e), 2 * (H // G)
+    k0 = ops.flex_source(kv, tile_elems=page, hdiv=per, hmul=PAGE * d, hmod=2, hmul2=dm, row_stride=d, length=dm, paged=True)
+    v = ops.flex_source(kv, tile_elems=page, const_off=G * PAGE * d, hdiv=per, hmul=PAGE * e, row_stride=e, length=e, paged=True)
+    maps = ops.attention_flex(q.view(n, 2 * H, dm), k0, ops.flex_source(), v, batch, scale, dv=e, window=window, keep_first=keep,
+                              out_dtype=torch.float32)
+    return ops.combine_maps(maps.view(n, H, 2, e), *combine, lib=(dm, e))
+
+
+def ragged_batch(lens, starts, pages):
+    lay = BatchLayout(len(lens), sum(lens), max(len(p) for p in pages), 0)
+    host = np.zeros(lay.size, dtype=np.int32)
+    fill_host(lay, host, tokens=[[0] * n for n in lens], starts=starts, slots=list(range(1, len(lens) + 1)), pages=pages,
+              want=[[] for _ in lens])
+    return StepBatch(lay, torch.from_numpy(host).to(DEV), q_lens=lens, starts=starts)
+
+
+@pytest.mark.parametrize("H,G,dm,e,window,keep", [(4, 2, 16, 32, 21, 5), (2, 1, 32, 64, 64, 0), (2, 2, 64, 128, 0, 0), (3, 1, 16, 16, 100, 70)])
+def test_two_maps_on_the_tensor_cores(H, G, dm, e, window, keep):
+    """Prompts (whole, ragged batches, later portions over cached keys) through the tensor-core kernel against the plain form."""
+    g = torch.Generator().manual_seed(9)
+    m = 300
+    q = torch.randn(m, H, 2, dm, generator=g).to(torch.bfloat16)
+    k = torch.randn(m, G, 2, dm, generator=g).to(torch.bfloat16)
+    v = torch.randn(m, G, e, generator=g).to(torch.bfloat16)
+    pages = [3, 1, 4, 2, 5]
+    kv = fill_pages(k.reshape(m, G, 2 * dm), v, pages, 12, torch.bfloat16).to(DEV)
+    comb = (0.45, 1e-5, 0.65)
+    ref = plain_two_maps(q.double(), k.double(), v.double(), 0.2, window, keep, *comb)
+    for start, n in ((0, 300), (0, 64), (0, 65), (37, 100), (128, 172), (299, 1)):
+        b = seq_batch(n, start, pages[:(start + n + PAGE - 1) // PAGE])
+        out = flex_two_maps(q[start:start + n].reshape(n, H, 2 * dm).to(DEV), kv, b, 0.2, H, G, dm, e, window, keep, comb)
+        close(out, ref[start:start + n], "bfloat16", f"{n} tokens after {start}", 3e-2)
+    # three requests in one step: the same rows at other places of the cache, one of them a later portion
+    kv2 = torch.full_like(kv, float("nan"))
+    lens, starts, pgs = [70, 130, 100], [0, 0, 200], [[6, 7], [8, 9, 10], [3, 1, 4, 2, 5]]
+    for src, dst in ((3, 6), (1, 7), (3, 8), (1, 9), (4, 10), (3, 3), (1, 1), (4, 4), (2, 2), (5, 5)):
+        kv2[dst] = kv[src]
+    b = ragged_batch(lens, starts, pgs)
+    qq = torch.cat([q[:70], q[:130], q[200:300]]).reshape(300, H, 2 * dm).to(DEV)
+    out = flex_two_maps(qq, kv2, b, 0.2, H, G, dm, e, window, keep, comb)
+    close(out, torch.cat([ref[:70], ref[:130], ref[200:300]]), "bfloat16", "a ragged step", 3e-2)
+
+
+@pytest.mark.parametrize("window,keep", [(50, 0), (64, 7), (10, 64), (130, 66)])
+def test_a_key_that_stands_out_on_the_tensor_cores(window, keep):
+    """As above, through the tensor-core kernel: key j's marker is the result exactly when j is visible."""
+    H, G, dm, e, n = 1, 1, 16, 16, 5 * 64 + 9
+    hit = 1.0 / math.sqrt(1.0 / e + 1e-6)
+    pages = [2, 1, 3, 4, 6, 5]
+    for j in (0, keep - 1, keep, 63, 64, 100, 128, 200):
+        if j < 0:
+            continue
+        q = torch.zeros(n, H, 2 * dm)
+        q[:, :, 0] = 1.0
+        k = torch.zeros(n, G, 2 * dm)
+        k[j, 0, 0] = 60.0
+        v = torch.zeros(n, G, e)
+        v[j, 0, 0] = 1.0
+        kv = fill_pages(k, v, pages, 7, torch.bfloat16).to(DEV)
+        sees = lambda i: j <= i and (i - j < window or j < keep)
+        for start in (0, 70):                                # a prompt from position 0, and a portion after 70 cached tokens
+            b = seq_batch(n - start, start, pages)
+            out = flex_two_maps(q[start:].to(torch.bfloat16).to(DEV), kv, b, 1.0, H, G, dm, e, window, keep, (0.0, 1e-6, 1.0)).float().cpu()
+            for i in range(start, n):
+                assert abs(out[i - start, 0, 0].item() - (hit if sees(i) else 0.0)) < 3e-2, (window, keep, j, start, i, out[i - start, 0, 0].item())
+
+
+@pytest.mark.parametrize("H,d,dr,e,window", [(2, 16, 16, 16, 50), (3, 64, 32, 64, 0), (2, 128, 64, 128, 130)])
+def test_keys_of_two_parts_from_the_steps_own_rows(H, d, dr, e, window):
+    """The tensor-core kernel over flat arrays: a head's key is its own part followed by a part all heads share; a sink; a
+    gate on the result; two requests in a step."""
+    g = torch.Generator().manual_seed(10)
+    lens = [150, 201]
+    n = sum(lens)
+    q = torch.randn(n, H, d + dr, generator=g).to(torch.bfloat16)
+    kvx = torch.randn(n, H * d + H * e, generator=g).to(torch.bfloat16)
+    kr = torch.randn(n, dr, generator=g).to(torch.bfloat16)
+    sink, gate = torch.randn(H, generator=g), torch.rand(n, H, generator=g)
+    b = ragged_batch(lens, [0, 0], [[1, 2, 3], [4, 5, 6, 7]])
+    k0 = ops.flex_source(kvx.to(DEV), hmul=d, row_stride=H * (d + e), length=d)
+    kvd = kvx.to(DEV)
+    krd = kr.to(DEV)
+    k0 = ops.flex_source(kvd, hmul=d, row_stride=H * (d + e), length=d)
+    out = ops.attention_flex(q.to(DEV), k0, ops.flex_source(krd, row_stride=dr, length=dr),
+                             ops.flex_source(kvd, const_off=H * d, hmul=e, row_stride=H * (d + e), length=e), b, 0.1, dv=e,
+                             window=window, sink=sink.to(DEV), gate=gate.to(DEV))
+    at = 0
+    for L in lens:
+        qq, kk = q[at:at + L].double(), kvx[at:at + L].double()
+        keys = torch.cat([kk[:, :H * d].reshape(L, H, d), kr[at:at + L].double()[:, None, :].expand(L, H, dr)], -1)
+        vals = kk[:, H * d:].reshape(L, H, e)
+        s = torch.einsum("ihd,jhd->hij", qq, keys) * 0.1
+        w = P.softmax_visible(s, P.window_visible(L, window or None), sink.double())
+        ref = torch.einsum("hij,jhe->ihe", w, vals) * gate[at:at + L].double()[:, :, None]
+        close(out[at:at + L], ref, "bfloat16", f"request of {L} tokens", 3e-2)
+        at += L
+    # a key that stands out is seen from its window's positions only
+    if window:
+        j = 77
+        q2 = torch.zeros(n, H, d + dr)
+        q2[:, :, 0] = 1.0
+        kv2 = torch.zeros(n, H * d + H * e)
+        kv2[j, 0] = 60.0                                        # head 0's own key part
+        kv2[j, H * d] = 1.0                                     # head 0's value
+        kv2d, kr2d = kv2.to(torch.bfloat16).to(DEV), torch.zeros(n, dr, dtype=torch.bfloat16, device=DEV)
+        out = ops.attention_flex(q2.to(torch.bfloat16).to(DEV), ops.flex_source(kv2d, hmul=d, row_stride=H * (d + e), length=d),
+                                 ops.flex_source(kr2d, row_stride=dr, length=dr),
+                                 ops.flex_source(kv2d, const_off=H * d, hmul=e, row_stride=H * (d + e), length=e), b, 1.0, dv=e,
+                                 window=window, sink=torch.full((H,), -3.0, device=DEV)).float().cpu()
+        for i in range(lens[0]):
+            assert abs(out[i, 0, 0].item() - (1.0 if 0 <= i - j < window else 0.0)) < 2e-2, (i, out[i, 0, 0].item())
+        assert out[lens[0]:, 0, 0].abs().max().item() == 0.0     # the other request sees none of it
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_long_prompts_take_the_tensor_core_kernels(graphs):
+    """Sizes the tensor-core prompt kernels take: prompts from position 0 alone and in a ragged step, then later portions and
+    single tokens over what they cached, launched and replayed from captured steps."""
+    name = "TC"
+    calls = []
+    orig = ops.attention_flex
+    ops.attention_flex = lambda *a, **k: calls.append(1) or orig(*a, **k)
+    try:
+        eng = engine(name, "bfloat16", max_tokens=4096, use_graphs=graphs)
+        toks = [random_tokens(CONFIGS[name]["vocab"], n, seed=80 + n) for n in (700, 90, 333)]
+        refs = [plain(name, t) for t in toks]
+        s = eng.open_seq()
+        close(eng.step([s], [toks[0][:600]], [list(range(600))]), refs[0][:600], "bfloat16", "a prompt of 600 tokens")
+        assert len(calls) == 3, "every layer's attention of a long prompt runs on the tensor cores"
+        close(eng.step([s], [toks[0][600:690]], [list(range(90))]), refs[0][600:690], "bfloat16", "a later portion")
+        rows = [eng.step([s], [[t]]).clone() for t in toks[0][690:]]
+        close(torch.cat(rows), refs[0][690:], "bfloat16", "decoded")
+        eng.close_seq(s)
+        slots = [eng.open_seq() for _ in toks]
+        cut = [650, 80, 300]
+        out = eng.step(slots, [t[:c] for t, c in zip(toks, cut)], [list(range(c)) for c in cut])
+        close(out, torch.cat([r[:c] for r, c in zip(refs, cut)]), "bfloat16", "a ragged step")
+        for i in range(10):
+            out = eng.step(slots, [[t[c + i]] for t, c in zip(toks, cut)])
+            close(out, torch.stack([r[c + i] for r, c in zip(refs, cut)]), "bfloat16", f"decode step {i}")
+    finally:
+        ops.attention_flex = orig
+
+
 # ---------------------------------------------------------------------------
 # whole models through the engine
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -318,7 +318,8 @@ __global__ void __launch_bounds__(256)
 latent_finish_kernel(const float* __restrict__ parts, int splits, int64_t split_stride, int qr, int r, int dr, int Hg,
                      const float* __restrict__ q_w, const float* __restrict__ kv_w, float eps,
                      const float* __restrict__ cos_t, const float* __restrict__ sin_t, int pairing, T* __restrict__ cq_out,
-                     float* __restrict__ gate_out, T* __restrict__ rows, const int* __restrict__ page_table, int table_width,
+                     float* __restrict__ gate_out, T* __restrict__ rows, T* __restrict__ flat_c, T* __restrict__ flat_kr,
+                     const int* __restrict__ page_table, int table_width,
                      const int* __restrict__ seq_of_token, const int* __restrict__ positions) {
     extern __shared__ float row[];
     __shared__ float red[40];
@@ -349,7 +350,11 @@ latent_finish_kernel(const float* __restrict__ parts, int splits, int64_t split_
             const int pos = positions[t];
             const int pg = page_table[(int64_t)seq_of_token[t] * table_width + pos / kPage];
             T* dst = rows + ((int64_t)pg * kPage + pos % kPage) * (r + dr);
-            for (int j = tid; j < r; j += blockDim.x) st(dst + j, (row[qr + j] * fc) * kv_w[j]);
+            for (int j = tid; j < r; j += blockDim.x) {
+                const float c = (row[qr + j] * fc) * kv_w[j];
+                st(dst + j, c);
+                if (flat_c) st(flat_c + (int64_t)t * r + j, c);
+            }
             const int half = dr >> 1;
             const float* kr = row + qr + r;
             for (int i = tid; i < half; i += blockDim.x) {
@@ -363,11 +368,59 @@ latent_finish_kernel(const float* __restrict__ parts, int splits, int64_t split_
                 }
                 st(dst + r + j0, u);
                 st(dst + r + j1, v);
+                if (flat_kr) {
+                    st(flat_kr + (int64_t)t * dr + j0, u);
+                    st(flat_kr + (int64_t)t * dr + j1, v);
+                }
             }
-            if ((dr & 1) && tid == 0) st(dst + r + dr - 1, kr[dr - 1]);
+            if ((dr & 1) && tid == 0) {
+                st(dst + r + dr - 1, kr[dr - 1]);
+                if (flat_kr) st(flat_kr + (int64_t)t * dr + dr - 1, kr[dr - 1]);
+            }
         }
     }
     for (int j = tid; j < Hg; j += blockDim.x) gate_out[(int64_t)t * Hg + j] = 1.0f / (1.0f + expf(-row[qr + r + dr + j]));
+}
+
+// ---------------------------------------------------------------------------
+// The queries as they are, for kernels that score them against keys made from the latent: the partial sums are
+// added up, the last dr numbers of every head [d | dr] are turned, and the row goes out in the activation type.
+template <typename T>
+__global__ void __launch_bounds__(256)
+latent_query_kernel(const float* __restrict__ parts, int splits, int64_t split_stride, int H, int d, int dr,
+                    const float* __restrict__ cos_t, const float* __restrict__ sin_t, int pairing, T* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
+    parts = fresh(parts);
+    cos_t = fresh(cos_t);
+    sin_t = fresh(sin_t);
+    const int t = blockIdx.x, dq = d + dr, half = dr >> 1, per = d + half + (dr & 1);     // work items of a head: plain numbers, pairs
+    const int64_t at = (int64_t)t * H * dq;
+    auto sum = [&](int j) {
+        float v = parts[at + j];
+        for (int s = 1; s < splits; ++s) v += parts[s * split_stride + at + j];
+        return v;
+    };
+    for (int idx = threadIdx.x; idx < H * per; idx += blockDim.x) {
+        const int h = idx / per, i = idx - h * per;
+        if (i < d) {
+            st(out + at + h * dq + i, sum(h * dq + i));
+        } else if (i - d < half) {
+            const int p = i - d;
+            const int j0 = h * dq + d + (pairing == 0 ? 2 * p : p), j1 = h * dq + d + (pairing == 0 ? 2 * p + 1 : p + half);
+            float u = sum(j0), v = sum(j1);
+            if (cos_t) {
+                const float cs = cos_t[(int64_t)t * half + p], sn = sin_t[(int64_t)t * half + p];
+                const float ru = u * cs - v * sn, rv = v * cs + u * sn;
+                u = ru;
+                v = rv;
+            }
+            st(out + at + j0, u);
+            st(out + at + j1, v);
+        } else {
+            st(out + at + h * dq + dq - 1, sum(h * dq + dq - 1));
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -528,7 +581,8 @@ int attn_multi(const void* q, const void* store, void* out, float* partial, cons
 template <typename T>
 int latent_finish(const float* parts, int splits, int n, int qr, int r, int dr, int Hg, const float* q_w, const float* kv_w,
                   float eps, const float* cos_t, const float* sin_t, int pairing, void* cq_out, float* gate_out, void* rows,
-                  const int* page_table, int table_width, const int* seq_of_token, const int* positions, cudaStream_t s) {
+                  void* flat_c, void* flat_kr, const int* page_table, int table_width, const int* seq_of_token, const int* positions,
+                  cudaStream_t s) {
     WICK_REQUIRE(qr > 0 && r >= 0 && dr >= 0 && Hg >= 0 && splits >= 1, "latent_finish: bad sizes");
     WICK_REQUIRE((cos_t == nullptr) == (sin_t == nullptr), "latent_finish: the two angle tables come together");
     WICK_REQUIRE(!rows || (r > 0 && kv_w), "latent_finish: a cache row needs the latent and its norm weight");
@@ -537,7 +591,8 @@ int latent_finish(const float* parts, int splits, int n, int qr, int r, int dr, 
     const size_t smem = (size_t)W * sizeof(float);
     WICK_REQUIRE(smem <= 48 * 1024, "latent_finish: a row of %d numbers is beyond one block's shared memory", W);
     WICK_CUDA(launch(latent_finish_kernel<T>, dim3(n), dim3(256), smem, s, parts, splits, (int64_t)n * W, qr, r, dr, Hg, q_w, kv_w, eps,
-                     cos_t, sin_t, pairing, (T*)cq_out, gate_out, (T*)rows, page_table, table_width, seq_of_token, positions));
+                     cos_t, sin_t, pairing, (T*)cq_out, gate_out, (T*)rows, (T*)flat_c, (T*)flat_kr, page_table, table_width, seq_of_token,
+                     positions));
     return check_launch("latent_finish");
 }
 
@@ -552,6 +607,16 @@ int latent_absorb(const float* parts, int splits, const void* uk, int n, int H, 
     WICK_CUDA(launch(latent_absorb_kernel<T>, dim3(ceil_div(n, LAT_TT), H, min(64, ceil_div(r, 128))), dim3(128), smem, s, parts, splits,
                      (int64_t)n * H * (d + dr), (const T*)uk, n, H, d, dr, r, cos_t, sin_t, pairing, out));
     return check_launch("latent_absorb");
+}
+
+template <typename T>
+int latent_query(const float* parts, int splits, int n, int H, int d, int dr, const float* cos_t, const float* sin_t, int pairing,
+                 void* out, cudaStream_t s) {
+    WICK_REQUIRE(H > 0 && d > 0 && dr >= 0 && splits >= 1, "latent_query: bad sizes");
+    if (n == 0) return 0;
+    WICK_CUDA(launch(latent_query_kernel<T>, dim3(n), dim3(256), 0, s, parts, splits, (int64_t)n * H * (d + dr), H, d, dr, cos_t, sin_t,
+                     pairing, (T*)out));
+    return check_launch("latent_query");
 }
 
 template <typename T>
@@ -591,14 +656,18 @@ WICK_ATTN_MULTI(wick_attn_multi1_f32, float, float, float, 1)
     WICK_API int wick_latent_finish_##SUFFIX(const float* parts, int splits, int n, int qr, int r, int dr, int Hg,              \
                                              const float* q_w, const float* kv_w, float eps, const float* cos_t,                \
                                              const float* sin_t, int pairing, void* cq_out, float* gate_out, void* rows,        \
-                                             const int* page_table, int table_width, const int* seq_of_token,                   \
-                                             const int* positions, void* s) {                                                   \
+                                             void* flat_c, void* flat_kr, const int* page_table, int table_width,               \
+                                             const int* seq_of_token, const int* positions, void* s) {                          \
         return latent_finish<T>(parts, splits, n, qr, r, dr, Hg, q_w, kv_w, eps, cos_t, sin_t, pairing, cq_out, gate_out, rows,  \
-                                page_table, table_width, seq_of_token, positions, (cudaStream_t)s);                              \
+                                flat_c, flat_kr, page_table, table_width, seq_of_token, positions, (cudaStream_t)s);             \
     }                                                                                                                            \
     WICK_API int wick_latent_absorb_##SUFFIX(const float* parts, int splits, const void* uk, int n, int H, int d, int dr, int r, \
                                              const float* cos_t, const float* sin_t, int pairing, float* out, void* s) {        \
         return latent_absorb<T>(parts, splits, uk, n, H, d, dr, r, cos_t, sin_t, pairing, out, (cudaStream_t)s);                 \
+    }                                                                                                                            \
+    WICK_API int wick_latent_query_##SUFFIX(const float* parts, int splits, int n, int H, int d, int dr, const float* cos_t,     \
+                                            const float* sin_t, int pairing, void* out, void* s) {                               \
+        return latent_query<T>(parts, splits, n, H, d, dr, cos_t, sin_t, pairing, out, (cudaStream_t)s);                         \
     }                                                                                                                            \
     WICK_API int wick_latent_expand_##SUFFIX(const float* y, const void* uv, const float* gate, int n, int H, int e, int r,     \
                                              void* out, void* s) {                                                              \

@@ -717,12 +717,13 @@ def attention_multi(q: torch.Tensor, store: torch.Tensor, batch, scale: float, *
 def latent_finish(parts: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, gate_heads: int, *, dtype: torch.dtype,
                   q_weight: torch.Tensor, kv_weight: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor],
                   sin: Optional[torch.Tensor], pairing: str = "neighbours", rows: Optional[torch.Tensor],
-                  page_table: torch.Tensor, seq_of_token: torch.Tensor, positions: torch.Tensor):
+                  page_table: torch.Tensor, seq_of_token: torch.Tensor, positions: torch.Tensor, flat: bool = False):
     """From the float32 partial sums ``parts`` [splits, n, q_rank + kv_rank + rot_dim + gate_heads] of a latent
     attention's down-projections: the query latent rms(.) * q_weight -> [n, q_rank] in ``dtype``; the latent
     rms(.) * kv_weight and the key part, turned by the angles of ``cos`` / ``sin`` [n, rot_dim / 2], -> the token's
     row of ``rows`` (pages of [64][kv_rank + rot_dim]; None: nothing is stored); sigmoid of the gates -> float32
-    [n, gate_heads] (None if there are none).  Returns (query latent, gates)."""
+    [n, gate_heads] (None if there are none).  Returns (query latent, gates); with ``flat`` (and ``rows``) also the step's
+    own latents [n, kv_rank] and key parts [n, rot_dim] as arrays of their own, in ``dtype``."""
     _cuda("parts", parts, torch.float32)
     W = q_rank + kv_rank + rot_dim + gate_heads
     _need(parts.dim() == 3 and parts.shape[2] == W, f"parts must be [splits, n, {W}], is {tuple(parts.shape)}")
@@ -742,11 +743,98 @@ def latent_finish(parts: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, 
     cq = torch.empty((n, q_rank), dtype=dtype, device=parts.device)
     gate = torch.empty((n, gate_heads), dtype=torch.float32, device=parts.device) if gate_heads else None
     use_rot = cos is not None and rot_dim > 0
-    _layer().call(f"wick_latent_finish_{_dt(cq)}", "piiiiiippfppippppippp", _p(parts), parts.shape[0], n, q_rank, kv_rank, rot_dim,
+    flat_c = flat_kr = None
+    if flat and rows is not None:
+        flat_c = torch.empty((n, kv_rank), dtype=dtype, device=parts.device)
+        flat_kr = torch.empty((n, rot_dim), dtype=dtype, device=parts.device)
+    _layer().call(f"wick_latent_finish_{_dt(cq)}", "piiiiiippfppippppppippp", _p(parts), parts.shape[0], n, q_rank, kv_rank, rot_dim,
                   gate_heads, _p(q_weight), _p(kv_weight), float(eps), _p(cos) if use_rot else None, _p(sin) if use_rot else None,
-                  PAIRINGS[pairing], _p(cq), _p(gate), _p(rows), _p(page_table), page_table.shape[-1], _p(seq_of_token),
-                  _p(positions), _stream())
+                  PAIRINGS[pairing], _p(cq), _p(gate), _p(rows), _p(flat_c), _p(flat_kr), _p(page_table), page_table.shape[-1],
+                  _p(seq_of_token), _p(positions), _stream())
+    if flat:
+        return cq, gate, flat_c, flat_kr
     return cq, gate
+
+
+def latent_query(q_parts: torch.Tensor, heads: int, d: int, rot_dim: int, *, cos: Optional[torch.Tensor],
+                 sin: Optional[torch.Tensor], pairing: str = "neighbours", dtype: torch.dtype) -> torch.Tensor:
+    """A latent attention's queries as they are: the float32 partial sums [splits, n, heads * (d + rot_dim)] added up, the
+    last ``rot_dim`` numbers of every head turned by the angles, in ``dtype`` [n, heads, d + rot_dim]."""
+    _cuda("q_parts", q_parts, torch.float32)
+    W = heads * (d + rot_dim)
+    _need(q_parts.dim() == 3 and q_parts.shape[2] == W, f"q_parts must be [splits, n, {W}], is {tuple(q_parts.shape)}")
+    n = q_parts.shape[1]
+    use_rot = cos is not None and rot_dim > 0
+    if use_rot:
+        _cuda("cos", cos, torch.float32, (n, rot_dim // 2))
+        _cuda("sin", sin, torch.float32, (n, rot_dim // 2))
+    out = torch.empty((n, heads, d + rot_dim), dtype=dtype, device=q_parts.device)
+    _layer().call(f"wick_latent_query_{_dt(out)}", "piiiiippipp", _p(q_parts), q_parts.shape[0], n, heads, d, rot_dim,
+                  _p(cos) if use_rot else None, _p(sin) if use_rot else None, PAIRINGS[pairing], _p(out), _stream())
+    return out
+
+
+# ---- prompt attention on the tensor cores with keys and values described by strides ---------------------------------
+def _flex(dk: int, dv: int) -> _Lib:
+    key = f"flex{dk}_{dv}"
+    lib = _libs.get(key)
+    if lib is None:
+        lib = _libs[key] = _Lib(f"wick_attn_flex_k{dk}_v{dv}", ["attn_flex.cu"], [f"WICK_DK={dk}", f"WICK_DV={dv}"])
+    return lib
+
+
+def attention_flex_supported(dk: int, dv: int, dtype: torch.dtype) -> bool:
+    """Whether :func:`attention_flex` takes query / key vectors of ``dk`` and values of ``dv`` numbers."""
+    return (dtype == torch.bfloat16 and not PLAIN_KERNELS and dk % 16 == 0 and 16 <= dk <= 256 and dv % 16 == 0
+            and 16 <= dv <= 128)
+
+
+def flex_source(t: Optional[torch.Tensor] = None, *, tile_elems: int = 0, const_off: int = 0, hdiv: int = 1, hmul: int = 0,
+                hmod: int = 1, hmul2: int = 0, row_stride: int = 0, length: int = 0, paged: bool = False) -> List[int]:
+    """Where the rows of one source of :func:`attention_flex` lie.  A tile of 64 keys of sequence b for head h starts at
+    ``page_table[b][tile] * tile_elems`` (paged) or at ``(first token of b + 64 tile) * row_stride`` (flat: one row per
+    token of the step), plus ``const_off + (h // hdiv) * hmul + (h % hmod) * hmul2``; rows are ``row_stride`` apart and
+    give ``length`` numbers.  All in elements of bfloat16."""
+    return [0 if t is None else t.data_ptr(), tile_elems, const_off, hdiv, hmul, hmod, hmul2, row_stride, length, 1 if paged else 0]
+
+
+def attention_flex(q: torch.Tensor, k0: List[int], k1: List[int], v: List[int], batch, scale: float, *, dv: int, window: int = 0,
+                   keep_first: int = 0, sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                   out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """Attention of a prompt's tokens on the tensor cores.  q: bfloat16 [n, heads, dk]; a key row is ``k0``'s numbers
+    followed by ``k1``'s (sources as :func:`flex_source` makes them; flat sources need sequences that start at position
+    0), a value row ``v``'s.  Visible to the query at position p: the keys j <= p with p - j < window or j < keep_first
+    (window 0: every j <= p).  ``sink`` float32 [heads]; ``gate`` float32 [n, heads], a factor of the bfloat16 result.
+    Returns [n, heads, dv] in ``out_dtype`` (float32 or bfloat16)."""
+    import numpy as np
+    _cuda("q", q, torch.bfloat16)
+    n, heads, dk = q.shape
+    _need(n == batch.n_tokens, f"q has {n} rows, the batch {batch.n_tokens} tokens")
+    _need(attention_flex_supported(dk, dv, q.dtype), f"no tensor-core attention for vectors of {dk} and values of {dv} numbers")
+    if sink is not None:
+        _cuda("sink", sink, torch.float32, (heads,))
+    if gate is not None:
+        _cuda("gate", gate, torch.float32, (n, heads))
+        _need(out_dtype == torch.bfloat16, "the gate is a factor of the bfloat16 result")
+    out = torch.empty((n, heads, dv), dtype=out_dtype, device=q.device)
+    src = np.asarray(k0 + k1 + v, dtype=np.int64)
+    _flex(dk, dv).call("wick_attn_flex_bf16", "pppppppippiiiiifp", _p(q), src.ctypes.data, _p(out) if out_dtype == torch.float32 else None,
+                       _p(out) if out_dtype == torch.bfloat16 else None, _p(gate), _p(sink), _p(batch.cu_seqlens), batch.n_seqs,
+                       _p(batch.start), _p(batch.page_table), batch.table_width, attention_tiles(batch), heads, int(window),
+                       int(keep_first), float(scale), _stream())
+    return out
+
+
+def combine_maps(a: torch.Tensor, lam: float, eps: float, factor: float, *, lib: Tuple[int, int]) -> torch.Tensor:
+    """a: float32 [n, H, 2, e], two maps' results a head.  Returns bfloat16 [n, H, e]: y = a_1 - lam a_2, then
+    y / sqrt(mean(y^2) + eps) * factor over e.  ``lib``: the (dk, dv) of the attention library that made ``a``."""
+    _cuda("a", a, torch.float32)
+    n, H, two, e = a.shape
+    _need(two == 2, "two maps a head")
+    out = torch.empty((n, H, e), dtype=torch.bfloat16, device=a.device)
+    _flex(*lib).call("wick_combine_maps_bf16", "pplifffp", _p(a), _p(out), n * H, e, float(lam), float(eps),
+                     float(factor), _stream())
+    return out
 
 
 def latent_absorb(q_parts: torch.Tensor, uk: torch.Tensor, heads: int, d: int, rot_dim: int, kv_rank: int, *,

@@ -34,6 +34,7 @@ import math
 import torch
 
 from .. import ops
+from ..layout import PAGE
 from ..models.spec import PartSpec
 from .attention import RotaryPairs
 from .base import CacheNeed, Mixer, TensorSpec, build_part, register_part
@@ -44,6 +45,7 @@ from .standard import NoPosition
 class DifferentialAttention(Mixer):
     PROMPT_CAPTURABLE = True
     MAPS = 2
+    TENSOR_CORES_FROM = 16      # tokens of a prompt step from which its attention takes the tensor-core kernel
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
@@ -124,9 +126,22 @@ class DifferentialAttention(Mixer):
                            cos=cos, sin=sin, rot_dims=rot.dims if rot else 0, pairing=rot.pairing if rot else "neighbours",
                            maps=self.MAPS, kv=cache.kv, page_table=batch.page_table, seq_of_token=batch.seq_of_token,
                            positions=batch.positions, write_kv=write_cache)
-        att = ops.attention_multi(q, cache.kv, batch, self.scale, maps=self.MAPS, kv_heads=self.kv_heads, v_dim=self.v_dim,
-                                  window=self.window, keep_first=self.keep_first,
-                                  combine=(self.lam, self.eps, 1.0 - self.diff), out_dtype=self.ctx.dtype)
+        combine = (self.lam, self.eps, 1.0 - self.diff)
+        if n >= self.TENSOR_CORES_FROM and not batch.is_decode and ops.attention_flex_supported(self.map_dim, self.v_dim, self.ctx.dtype):
+            # a prompt's tokens: every map of every head is a head of its own for the tensor-core kernel (its keys one
+            # half of a cached key row, its values the head's), and a second kernel combines the two results of a head
+            G, d, e = self.kv_heads, self.head_dim, self.v_dim
+            page, per = G * PAGE * (d + e), self.MAPS * (self.heads // G)
+            k0 = ops.flex_source(cache.kv, tile_elems=page, hdiv=per, hmul=PAGE * d, hmod=self.MAPS, hmul2=self.map_dim,
+                                 row_stride=d, length=self.map_dim, paged=True)
+            v = ops.flex_source(cache.kv, tile_elems=page, const_off=G * PAGE * d, hdiv=per, hmul=PAGE * e, row_stride=e, length=e,
+                                paged=True)
+            maps = ops.attention_flex(q.view(n, self.MAPS * self.heads, self.map_dim), k0, ops.flex_source(), v, batch, self.scale,
+                                      dv=e, window=self.window, keep_first=self.keep_first, out_dtype=torch.float32)
+            att = ops.combine_maps(maps.view(n, self.heads, self.MAPS, e), *combine, lib=(self.map_dim, e))
+        else:
+            att = ops.attention_multi(q, cache.kv, batch, self.scale, maps=self.MAPS, kv_heads=self.kv_heads, v_dim=self.v_dim,
+                                      window=self.window, keep_first=self.keep_first, combine=combine, out_dtype=self.ctx.dtype)
         return self.o.forward_delta(att.view(n, self.heads * self.v_dim))
 
 

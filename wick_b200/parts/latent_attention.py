@@ -28,12 +28,17 @@ elements, values of size e, latent of r numbers):
 A layer with ``own_kv`` False has no Wdkv: it is scheduled to read the cache of an earlier
 layer, and applies its own Wuk and Wuv to that layer's rows.
 
-The kernels never expand a cached row into keys and values: since q_i . (Wuk_i c) =
+Two forms compute this.  A step over cached rows (decoding, a prompt's later portion, the
+32-bit path) never expands a row into keys and values: since q_i . (Wuk_i c) =
 (Wuk_i^T q_i) . c, a head's query is carried into the latent's space once per token
 ([Wuk_i^T q_i | rotated q_i], r + dr numbers), the attention runs over the cached rows
 themselves as one shared key head whose first r numbers are also the value, and Wuv_i is
-applied to the weighted sum of rows.  Query in latent space, scores, weights and the sum
-are float32.
+applied to the weighted sum of rows; query in latent space, scores, weights and the sum
+are float32.  A bfloat16 prompt from position 0 (launched, not replayed from a captured
+step) makes the step's own keys and values once, [Wuk; Wuv] c as one matrix product, and
+runs the tensor-core attention over them and the shared key part, with the gate in its
+epilogue; the layer that owns the rows leaves the step's latents in the step's memo for a
+layer that reads its cache.
 """
 from __future__ import annotations
 
@@ -79,6 +84,7 @@ class LatentAttention(Mixer):
         self.uq = Linear(self.heads * (self.head_dim + self.rot_dim), self.q_rank, ctx)
         self.o = Linear(self.width, self.heads * self.v_dim, ctx)
         self.uk = self.uv = self.q_weight = self.kv_weight = self.sink = None
+        self.ukv = Linear(self.heads * (self.head_dim + self.v_dim), self.kv_rank, ctx)     # [Wuk; Wuv] for prompts
 
     def tensor_specs(self):
         nm, H = self.names, self.heads
@@ -101,6 +107,10 @@ class LatentAttention(Mixer):
         self.uq.load_rows([fetch(nm["uq"])])
         self.o.load_rows([fetch(nm["o"])])
         self.uk, self.uv = hold(fetch(nm["uk"]), "matrix"), hold(fetch(nm["uv"]), "matrix")
+        self.expands = ops.attention_flex_supported(self.head_dim + self.rot_dim, self.v_dim, self.ctx.dtype) and self.uk.is_cuda \
+            and self.head_dim % 8 == 0 and self.rot_dim % 8 == 0 and self.kv_rank % 8 == 0
+        if self.expands:                                   # (held a second time, in the matrix product's own layout)
+            self.ukv.use(torch.cat([self.uk, self.uv], 0))
         self.q_weight = hold(fetch(nm["dq_norm"]), "vector")
         self.kv_weight = hold(fetch(nm["dkv_norm"]), "vector") if self.own_kv else None
         self.sink = hold(fetch(nm["sink"]), "vector") if self.has_sink else None
@@ -132,6 +142,14 @@ class LatentAttention(Mixer):
         return self.down.weight_bytes() + self.uq.weight_bytes() + self.o.weight_bytes() + \
             self.heads * (self.head_dim + self.v_dim) * self.kv_rank * el
 
+    TENSOR_CORES_FROM = 16      # tokens of a prompt step from which its attention takes the tensor-core kernel
+
+    def _from_position_zero(self, batch) -> bool:
+        """Whether the step is a launched prompt step whose sequences all start at position 0 (a captured step's host
+        lists describe no real prompt: it takes the other form)."""
+        return (not batch.is_decode and batch.q_tiles is None and batch.n_tokens >= self.TENSOR_CORES_FROM
+                and all(s == 0 for s in batch.starts))
+
     def forward(self, x, batch, cache, write_cache):
         n, H = x.shape[0], self.heads
         if cache is None or getattr(cache, "rows", None) is None:
@@ -139,12 +157,28 @@ class LatentAttention(Mixer):
         parts = self.down.forward_delta(x)                # float32 [splits, n, q_rank (+ r + dr) (+ H)]
         rot = self.position if isinstance(self.position, RotaryPairs) else None
         cos, sin = rot.tables(batch) if rot else (None, None)
-        cq, gate = ops.latent_finish(parts, self.q_rank, self.kv_rank if self.own_kv else 0, self.rot_dim if self.own_kv else 0,
-                                     H if self.has_gate else 0, dtype=self.ctx.dtype, q_weight=self.q_weight,
-                                     kv_weight=self.kv_weight, eps=self.eps, cos=cos, sin=sin,
-                                     rows=cache.rows if write_cache and self.own_kv else None, page_table=batch.page_table,
-                                     seq_of_token=batch.seq_of_token, positions=batch.positions)
+        expand = self.expands and self._from_position_zero(batch)
+        memo_key = ("latent_rows", cache.rows.data_ptr())
+        writes = write_cache and self.own_kv
+        res = ops.latent_finish(parts, self.q_rank, self.kv_rank if self.own_kv else 0, self.rot_dim if self.own_kv else 0,
+                                H if self.has_gate else 0, dtype=self.ctx.dtype, q_weight=self.q_weight,
+                                kv_weight=self.kv_weight, eps=self.eps, cos=cos, sin=sin,
+                                rows=cache.rows if writes else None, page_table=batch.page_table,
+                                seq_of_token=batch.seq_of_token, positions=batch.positions, flat=writes and self._from_position_zero(batch))
+        cq, gate = res[0], res[1]
+        if len(res) == 4:
+            batch.memo[memo_key] = (res[2], res[3])       # the step's own latents and key parts, for this layer and its readers
         q = self.uq.forward_delta(cq)                     # float32 [splits, n, H (d + dr)]
+        if expand and memo_key in batch.memo:
+            c, kr = batch.memo[memo_key]
+            d, e, dr = self.head_dim, self.v_dim, self.rot_dim
+            qb = ops.latent_query(q, H, d, dr, cos=cos, sin=sin, dtype=self.ctx.dtype)
+            kv = self.ukv.forward(c, self.ctx.dtype)      # [n, H d + H e]: every head's unrotated keys, then every head's values
+            k0 = ops.flex_source(kv, hmul=d, row_stride=H * (d + e), length=d)
+            k1 = ops.flex_source(kr, row_stride=dr, length=dr) if dr else ops.flex_source()
+            v = ops.flex_source(kv, const_off=H * d, hmul=e, row_stride=H * (d + e), length=e)
+            out = ops.attention_flex(qb, k0, k1, v, batch, self.scale, dv=e, window=self.window, sink=self.sink, gate=gate)
+            return self.o.forward_delta(out.view(n, H * e))
         q_lat = ops.latent_absorb(q, self.uk, H, self.head_dim, self.rot_dim, self.kv_rank, cos=cos, sin=sin)
         att = ops.attention_multi(q_lat, cache.rows, batch, self.scale, maps=1, kv_heads=1, v_dim=self.kv_rank,
                                   window=self.window, sink=self.sink, rows_of=self.row, out_dtype=torch.float32)
