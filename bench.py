@@ -490,6 +490,11 @@ def tuguvik_parts(torch, wick, pk, z, name, cfg_json):
         e = kw["v_dim"]
         return 2.0 * ctx["pairs"] * H * (d + kw["maps"] * e), nbytes(q, r) + ctx["kv_rows"] * store[0].numel() // 64 * store.element_size()
 
+    def attn_flex_work(r, q, k0, k1, v, batch, scale, **kw):
+        n, heads, dk = q.shape
+        row_bytes = 2 * (k0[8] + k1[8] + v[8]) * (heads if not k0[9] else 1)      # (flat sources hold every head's rows)
+        return 2.0 * ctx["pairs"] * heads * (dk + kw["dv"]), nbytes(q, r) + ctx["kv_rows"] * row_bytes
+
     def attn_std_work(r, q, kv, batch, *a, **k):
         n, H, d = q.shape
         return 4.0 * ctx["pairs"] * H * d, nbytes(q, r) + ctx["kv_rows"] * kv[0].numel() // 64 * kv.element_size()
@@ -508,7 +513,9 @@ def tuguvik_parts(torch, wick, pk, z, name, cfg_json):
     def norm_work(r, x, delta=None, *a, **k):
         return 0.0, nbytes(x, delta) + (nbytes(x) if delta is not None and k.get("rows") is None else 0) + (nbytes(r) if r is not None and r is not x else 0)
 
-    for fname, kind, work in (("attention_multi", "attention", attn_multi_work), ("attention_prompt", "attention", attn_std_work),
+    for fname, kind, work in (("attention_multi", "attention", attn_multi_work), ("attention_flex", "attention", attn_flex_work),
+                              ("combine_maps", "attention", rows_work), ("latent_query", "finish", rows_work),
+                              ("attention_prompt", "attention", attn_std_work),
                               ("attention_decode", "attention", attn_std_work), ("qkv_finish", "finish", rows_work),
                               ("latent_finish", "finish", rows_work), ("qk_norm_rope_append", "finish", rows_work),
                               ("latent_absorb", "query into the rows' space", absorb_work),
@@ -521,7 +528,7 @@ def tuguvik_parts(torch, wick, pk, z, name, cfg_json):
     for blk in eng.model.blocks:
         m = blk.mixer
         for attr, kind in (("qkv", "projections into the mixer"), ("down", "projections into the mixer"),
-                           ("uq", "projections into the mixer"), ("o", "o product")):
+                           ("uq", "projections into the mixer"), ("ukv", "keys and values from the latent"), ("o", "o product")):
             if isinstance(getattr(m, attr, None), Linear):
                 product(kind, getattr(m, attr))
         for attr in ("gate_up", "down"):

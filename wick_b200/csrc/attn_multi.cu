@@ -21,7 +21,7 @@
 
 namespace wick {
 
-constexpr int MV_CHUNKS = 4;                    // value sizes up to 512: a lane holds 4 neighbours of every 128
+constexpr int MV_MAX_CHUNKS = 4;                // value sizes up to 512: a lane holds 4 neighbours of every 128 (kernels are built for 1 and 4 such chunks)
 
 __device__ __forceinline__ void mv_load4(const float* p, float* v) {
     const float4 t = *reinterpret_cast<const float4*>(p);
@@ -46,7 +46,7 @@ __device__ __forceinline__ int visible_key(int v, int n_kept, int lo) { return v
 // With `partial` the fold's result goes there as a record (maximum, sum, two unused numbers, unnormalised values) per (token, head,
 // map, run) for the merge kernel; without, the block holds all visible keys and finishes itself: the sink joins,
 // the sums are divided, MAPS = 2 is combined (y_1 - lambda y_2, then the norm over the head's values).
-template <int MAPS>
+template <int MAPS, int MV_CHUNKS>
 __device__ __forceinline__ void finish_head(float (&y)[MAPS][4 * MV_CHUNKS], int lane, int e, float lam, float eps, float factor) {
     if (MAPS == 2) {
         float ss = 0.f;
@@ -66,7 +66,7 @@ __device__ __forceinline__ void finish_head(float (&y)[MAPS][4 * MV_CHUNKS], int
     }
 }
 
-template <typename T, typename TQ, typename TO, int MAPS, int GROUP>
+template <typename T, typename TQ, typename TO, int MAPS, int GROUP, int MV_CHUNKS>
 __global__ void __launch_bounds__(256)
 attn_multi_kernel(const TQ* __restrict__ q, const T* __restrict__ store, TO* __restrict__ out, float* __restrict__ partial,
                   const int* __restrict__ seq_of_token, const int* __restrict__ positions,
@@ -74,7 +74,7 @@ attn_multi_kernel(const TQ* __restrict__ q, const T* __restrict__ store, TO* __r
                   int k_row, int64_t v_off, int v_row, float scale, int window, int keep_first,
                   const float* __restrict__ sink, float lam, float eps, float factor) {
     constexpr int NQ = MAPS * GROUP;
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
     pdl_trigger();
     pdl_wait();
     q = fresh(q);
@@ -115,28 +115,38 @@ attn_multi_kernel(const TQ* __restrict__ q, const T* __restrict__ store, TO* __r
         float s[NQ], p[NQ];
 #pragma unroll
         for (int a = 0; a < NQ; ++a) s[a] = 0.f;
+        // where this lane's key row and value row lie (lanes beyond the run's end name its last key and weigh nothing)
+        const int key = visible_key(min(vi, v_end - 1), n_kept, lo);
+        const int64_t in_page = (int64_t)table[key / kPage] * page_elems, place = (int64_t)g * kPage + (key % kPage);
+        const int64_t v_at = in_page + v_off + place * v_row;
         if (valid) {
-            const int key = visible_key(vi, n_kept, lo);
-            const T* kp = store + (int64_t)table[key / kPage] * page_elems + ((int64_t)g * kPage + (key % kPage)) * k_row;
+            const T* kp = store + in_page + place * k_row;
 #pragma unroll
             for (int a = 0; a < MAPS; ++a) {
                 const T* ka = kp + a * dm;
                 if (k_vec) {
-                    for (int x = 0; x < dm; x += 2 * VN) {           // two loads of 16 bytes in flight
-                        Vec16<T> kk[2];
-                        kk[0].load(ka + x);
-                        const bool two = x + VN < dm;
-                        if (two) kk[1].load(ka + x + VN);
+                    for (int x = 0; x < dm; x += 4 * VN) {           // four loads of 16 bytes in flight
+                        Vec16<T> kk[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                            if (x + u * VN < dm) kk[u].load(ka + x + u * VN);
 #pragma unroll
                         for (int gi = 0; gi < GROUP; ++gi) {
                             const float* qa = qs + (gi * MAPS + a) * dm + x;
                             float dot = s[gi * MAPS + a];
 #pragma unroll
-                            for (int i = 0; i < VN; ++i) dot = fmaf(qa[i], kk[0].v[i], dot);
-                            if (two) {
+                            for (int u = 0; u < 4; ++u)
+                                if (x + u * VN < dm) {
+                                    // (the query's numbers four at a time: one trip to shared memory for four products)
 #pragma unroll
-                                for (int i = 0; i < VN; ++i) dot = fmaf(qa[VN + i], kk[1].v[i], dot);
-                            }
+                                    for (int i = 0; i < VN; i += 4) {
+                                        const float4 q4 = *reinterpret_cast<const float4*>(qa + u * VN + i);
+                                        dot = fmaf(q4.x, kk[u].v[i], dot);
+                                        dot = fmaf(q4.y, kk[u].v[i + 1], dot);
+                                        dot = fmaf(q4.z, kk[u].v[i + 2], dot);
+                                        dot = fmaf(q4.w, kk[u].v[i + 3], dot);
+                                    }
+                                }
                             s[gi * MAPS + a] = dot;
                         }
                     }
@@ -160,10 +170,14 @@ attn_multi_kernel(const TQ* __restrict__ q, const T* __restrict__ store, TO* __r
 #pragma unroll
             for (int c = 0; c < 4 * MV_CHUNKS; ++c) acc[a][c] *= corr;
         }
+        // the tile's value rows, each read by the whole warp; their places come from the lanes, so that the loads of
+        // several rows are in flight together (a chain of look-ups and loads, row after row, is what a step of few
+        // tokens would otherwise wait for)
         const int n_keys = min(32, v_end - v0);
-        for (int jj = 0; jj < n_keys; ++jj) {
-            const int key = visible_key(v0 + jj, n_kept, lo);
-            const T* vp = store + (int64_t)table[key / kPage] * page_elems + v_off + ((int64_t)g * kPage + (key % kPage)) * v_row;
+#pragma unroll 4
+        for (int jj = 0; jj < 32; ++jj) {
+            if (jj >= n_keys) break;
+            const T* vp = store + __shfl_sync(0xffffffffu, v_at, jj);
             float pj[NQ];
 #pragma unroll
             for (int a = 0; a < NQ; ++a) pj[a] = __shfl_sync(0xffffffffu, p[a], jj);
@@ -242,7 +256,7 @@ attn_multi_kernel(const TQ* __restrict__ q, const T* __restrict__ store, TO* __r
             }
         }
         if (partial) continue;
-        finish_head<MAPS>(y, lane, e, lam, eps, factor);
+        finish_head<MAPS, MV_CHUNKS>(y, lane, e, lam, eps, factor);
         TO* o = out + ((int64_t)t * H + h) * e;
 #pragma unroll
         for (int c = 0; c < MV_CHUNKS; ++c)
@@ -256,7 +270,7 @@ attn_multi_kernel(const TQ* __restrict__ q, const T* __restrict__ store, TO* __r
 
 // One warp per (token, head): the records of the runs of keys (a run that held no key has the maximum -inf) are
 // folded in run order, map by map; the sink joins; the sums are divided; two maps are combined.
-template <typename TO, int MAPS>
+template <typename TO, int MAPS, int MV_CHUNKS>
 __global__ void __launch_bounds__(128)
 attn_multi_merge_kernel(const float* __restrict__ partial, TO* __restrict__ out, int n_heads_total, int H, int e, int runs,
                         const float* __restrict__ sink, float lam, float eps, float factor) {
@@ -296,7 +310,7 @@ attn_multi_merge_kernel(const float* __restrict__ partial, TO* __restrict__ out,
 #pragma unroll
         for (int c = 0; c < 4 * MV_CHUNKS; ++c) y[a][c] *= inv;
     }
-    finish_head<MAPS>(y, lane, e, lam, eps, factor);
+    finish_head<MAPS, MV_CHUNKS>(y, lane, e, lam, eps, factor);
     TO* o = out + (int64_t)th * e;
 #pragma unroll
     for (int c = 0; c < MV_CHUNKS; ++c)
@@ -427,14 +441,14 @@ latent_query_kernel(const float* __restrict__ parts, int splits, int64_t split_s
 // One block per (TT tokens, head).  The head's query [d | dr] of each token is summed into shared memory;
 // thread j then makes element j of Wuk_h^T q for all TT tokens (a column of the head's d x r block of
 // Wuk, read once for the TT tokens; sums over the d rows in index order), and the turned dr numbers follow it.
-constexpr int LAT_TT = 8;
+constexpr int LAT_TT = 8;                       // (the kernels below spell out eight accumulators)
 
 template <typename T>
 __global__ void __launch_bounds__(256)
 latent_absorb_kernel(const float* __restrict__ parts, int splits, int64_t split_stride, const T* __restrict__ uk, int n, int H,
                      int d, int dr, int r, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int pairing,
                      float* __restrict__ out) {
-    extern __shared__ float qh[];                // [TT][d + dr]
+    extern __shared__ __align__(16) float qh[];   // [d + dr][TT]: a number of all TT tokens side by side
     pdl_trigger();
     pdl_wait();
     parts = fresh(parts);
@@ -447,15 +461,15 @@ latent_absorb_kernel(const float* __restrict__ parts, int splits, int64_t split_
         const int64_t at = (int64_t)(t0 + tt) * W + h * dq + x;
         float v = parts[at];
         for (int s = 1; s < splits; ++s) v += parts[s * split_stride + at];
-        qh[tt * dq + x] = v;
+        qh[x * LAT_TT + tt] = v;
     }
-    for (int idx = tid + n_t * dq; idx < LAT_TT * dq; idx += blockDim.x) qh[idx] = 0.f;
+    for (int idx = tid; idx < (LAT_TT - n_t) * dq; idx += blockDim.x) qh[(idx % dq) * LAT_TT + n_t + idx / dq] = 0.f;
     __syncthreads();
     const int half = dr >> 1;
     for (int idx = tid; idx < (blockIdx.z == 0 ? n_t * half : 0); idx += blockDim.x) {
         const int tt = idx / half, i = idx - tt * half;
         const int j0 = pairing == 0 ? 2 * i : i, j1 = pairing == 0 ? 2 * i + 1 : i + half;
-        float u = qh[tt * dq + d + j0], v = qh[tt * dq + d + j1];
+        float u = qh[(d + j0) * LAT_TT + tt], v = qh[(d + j1) * LAT_TT + tt];
         if (cos_t) {
             const float cs = cos_t[(int64_t)(t0 + tt) * half + i], sn = sin_t[(int64_t)(t0 + tt) * half + i];
             const float ru = u * cs - v * sn, rv = v * cs + u * sn;
@@ -466,7 +480,7 @@ latent_absorb_kernel(const float* __restrict__ parts, int splits, int64_t split_
         o[j0] = u;
         o[j1] = v;
     }
-    if ((dr & 1) && tid < n_t && blockIdx.z == 0) out[((int64_t)(t0 + tid) * H + h) * (r + dr) + r + dr - 1] = qh[tid * dq + d + dr - 1];
+    if ((dr & 1) && tid < n_t && blockIdx.z == 0) out[((int64_t)(t0 + tid) * H + h) * (r + dr) + r + dr - 1] = qh[(d + dr - 1) * LAT_TT + tid];
     const T* w = uk + (int64_t)h * d * r;
     for (int j = blockIdx.z * blockDim.x + tid; j < r; j += gridDim.z * blockDim.x) {      // (the blocks along z share the columns)
         float acc[LAT_TT];
@@ -474,8 +488,9 @@ latent_absorb_kernel(const float* __restrict__ parts, int splits, int64_t split_
         for (int tt = 0; tt < LAT_TT; ++tt) acc[tt] = 0.f;
         for (int x = 0; x < d; ++x) {
             const float wv = ld(w + (int64_t)x * r + j);
-#pragma unroll
-            for (int tt = 0; tt < LAT_TT; ++tt) acc[tt] = fmaf(qh[tt * dq + x], wv, acc[tt]);
+            const float4 qa = *reinterpret_cast<const float4*>(qh + x * LAT_TT), qb = *reinterpret_cast<const float4*>(qh + x * LAT_TT + 4);
+            acc[0] = fmaf(qa.x, wv, acc[0]); acc[1] = fmaf(qa.y, wv, acc[1]); acc[2] = fmaf(qa.z, wv, acc[2]); acc[3] = fmaf(qa.w, wv, acc[3]);
+            acc[4] = fmaf(qb.x, wv, acc[4]); acc[5] = fmaf(qb.y, wv, acc[5]); acc[6] = fmaf(qb.z, wv, acc[6]); acc[7] = fmaf(qb.w, wv, acc[7]);
         }
 #pragma unroll
         for (int tt = 0; tt < LAT_TT; ++tt)
@@ -490,7 +505,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 latent_expand_kernel(const float* __restrict__ y, const T* __restrict__ uv, const float* __restrict__ gate, int n, int H,
                      int e, int r, T* __restrict__ out) {
-    extern __shared__ float ys[];                // [TT][r]
+    extern __shared__ __align__(16) float ys[];   // [r][TT]: a number of all TT tokens side by side
     pdl_trigger();
     pdl_wait();
     y = fresh(y);
@@ -499,7 +514,7 @@ latent_expand_kernel(const float* __restrict__ y, const T* __restrict__ uv, cons
     const int n_t = min(LAT_TT, n - t0);
     for (int idx = tid; idx < LAT_TT * r; idx += blockDim.x) {
         const int tt = idx / r, j = idx - tt * r;
-        ys[idx] = tt < n_t ? y[((int64_t)(t0 + tt) * H + h) * r + j] : 0.f;
+        ys[j * LAT_TT + tt] = tt < n_t ? y[((int64_t)(t0 + tt) * H + h) * r + j] : 0.f;
     }
     __syncthreads();
     for (int x = blockIdx.z * n_warps + warp; x < e; x += gridDim.z * n_warps) {             // (the blocks along z share the rows)
@@ -509,8 +524,9 @@ latent_expand_kernel(const float* __restrict__ y, const T* __restrict__ uv, cons
         for (int tt = 0; tt < LAT_TT; ++tt) acc[tt] = 0.f;
         for (int j = lane; j < r; j += 32) {
             const float wv = ld(w + j);
-#pragma unroll
-            for (int tt = 0; tt < LAT_TT; ++tt) acc[tt] = fmaf(ys[tt * r + j], wv, acc[tt]);
+            const float4 ya = *reinterpret_cast<const float4*>(ys + j * LAT_TT), yb = *reinterpret_cast<const float4*>(ys + j * LAT_TT + 4);
+            acc[0] = fmaf(ya.x, wv, acc[0]); acc[1] = fmaf(ya.y, wv, acc[1]); acc[2] = fmaf(ya.z, wv, acc[2]); acc[3] = fmaf(ya.w, wv, acc[3]);
+            acc[4] = fmaf(yb.x, wv, acc[4]); acc[5] = fmaf(yb.y, wv, acc[5]); acc[6] = fmaf(yb.z, wv, acc[6]); acc[7] = fmaf(yb.w, wv, acc[7]);
         }
 #pragma unroll
         for (int tt = 0; tt < LAT_TT; ++tt) acc[tt] = warp_sum(acc[tt]);
@@ -526,7 +542,7 @@ latent_expand_kernel(const float* __restrict__ y, const T* __restrict__ uv, cons
 }
 
 // ---------------------------------------------------------------------------
-template <typename T, typename TQ, typename TO, int MAPS, int GROUP>
+template <typename T, typename TQ, typename TO, int MAPS, int GROUP, int MV_CHUNKS>
 int attn_multi_launch(const void* q, const void* store, void* out, float* partial, const int* seq_of_token, const int* positions,
                       const int* page_table, int table_width, int n, int H, int G, int dm, int e, int64_t page_elems, int k_row,
                       int64_t v_off, int v_row, float scale, int window, int keep_first, const float* sink, float lam, float eps,
@@ -537,15 +553,15 @@ int attn_multi_launch(const void* q, const void* store, void* out, float* partia
     WICK_REQUIRE(smem <= 160 * 1024, "attn_multi: heads of %d numbers are beyond one block's shared memory", NQ * dm);
     static size_t raised = 48 * 1024;
     if (smem > raised) {
-        WICK_CUDA(cudaFuncSetAttribute(attn_multi_kernel<T, TQ, TO, MAPS, GROUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        WICK_CUDA(cudaFuncSetAttribute(attn_multi_kernel<T, TQ, TO, MAPS, GROUP, MV_CHUNKS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
         raised = 160 * 1024;
     }
-    WICK_CUDA(launch(attn_multi_kernel<T, TQ, TO, MAPS, GROUP>, dim3((unsigned)(n * (H / GROUP)), runs), dim3(32 * warps), smem, s,
+    WICK_CUDA(launch(attn_multi_kernel<T, TQ, TO, MAPS, GROUP, MV_CHUNKS>, dim3((unsigned)(n * (H / GROUP)), runs), dim3(32 * warps), smem, s,
                      (const TQ*)q, (const T*)store, (TO*)out, partial, seq_of_token, positions, page_table, table_width, H, G, dm, e,
                      page_elems, k_row, v_off, v_row, scale, window, keep_first, sink, lam, eps, factor));
     if (int rc = check_launch("attn_multi")) return rc;
     if (partial) {
-        WICK_CUDA(launch(attn_multi_merge_kernel<TO, MAPS>, dim3(ceil_div((int64_t)n * H, 4)), dim3(128), 0, s, (const float*)partial,
+        WICK_CUDA(launch(attn_multi_merge_kernel<TO, MAPS, MV_CHUNKS>, dim3(ceil_div((int64_t)n * H, 4)), dim3(128), 0, s, (const float*)partial,
                          (TO*)out, n * H, H, e, runs, sink, lam, eps, factor));
         return check_launch("attn_multi_merge");
     }
@@ -561,20 +577,26 @@ int attn_multi(const void* q, const void* store, void* out, float* partial, cons
                int64_t v_off, int v_row, float scale, int window, int keep_first, const float* sink, float lam, float eps,
                float factor, int few, int runs, cudaStream_t s) {
     WICK_REQUIRE(H > 0 && G > 0 && H % G == 0 && dm > 0 && e > 0, "attn_multi: bad head counts or sizes");
-    WICK_REQUIRE(e <= 128 * MV_CHUNKS, "attn_multi: a value size of %d is beyond %d", e, 128 * MV_CHUNKS);
+    WICK_REQUIRE(e <= 128 * MV_MAX_CHUNKS, "attn_multi: a value size of %d is beyond %d", e, 128 * MV_MAX_CHUNKS);
     WICK_REQUIRE(window >= 0 && keep_first >= 0, "attn_multi: bad window");
     WICK_REQUIRE(runs >= 1 && runs <= 64 && (runs == 1 || partial), "attn_multi: %d runs of keys need a place for their records", runs);
     WICK_REQUIRE((int64_t)n * H <= 0x7fffffff, "attn_multi: too many (token, head) pairs");
     if (n == 0) return 0;
     if (runs == 1) partial = nullptr;
-    const int warps = few ? 8 : 1, per_kv = H / G;
-#define WICK_AM(GROUP)                                                                                                          \
-    return attn_multi_launch<T, TQ, TO, MAPS, GROUP>(q, store, out, partial, seq_of_token, positions, page_table, table_width, n, H, G, \
-                                                     dm, e, page_elems, k_row, v_off, v_row, scale, window, keep_first, sink, lam,   \
-                                                     eps, factor, warps, runs, s)
-    if (MAPS == 1 && few && per_kv % 4 == 0) WICK_AM(4);
-    if (MAPS == 1 && few && per_kv % 2 == 0) WICK_AM(2);
-    WICK_AM(1);
+    const int per_kv = H / G;
+    // (eight warps a block for a step of few tokens; four where the warps' results would fill a block's shared memory)
+#define WICK_AM(GROUP, CH)                                                                                                       \
+    return attn_multi_launch<T, TQ, TO, MAPS, GROUP, CH>(q, store, out, partial, seq_of_token, positions, page_table, table_width, n, H, \
+                                                         G, dm, e, page_elems, k_row, v_off, v_row, scale, window, keep_first, sink, \
+                                                         lam, eps, factor, few ? (GROUP * CH > 4 ? 4 : 8) : 1, runs, s)
+    if (e <= 128) {
+        if (MAPS == 1 && few && per_kv % 4 == 0) WICK_AM(4, 1);
+        if (MAPS == 1 && few && per_kv % 2 == 0) WICK_AM(2, 1);
+        WICK_AM(1, 1);
+    }
+    if (MAPS == 1 && few && per_kv % 4 == 0) WICK_AM(4, 4);
+    if (MAPS == 1 && few && per_kv % 2 == 0) WICK_AM(2, 4);
+    WICK_AM(1, 4);
 #undef WICK_AM
 }
 

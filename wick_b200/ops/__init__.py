@@ -694,7 +694,7 @@ def attention_multi(q: torch.Tensor, store: torch.Tensor, batch, scale: float, *
     # A step of few tokens: eight warps a block, heads that read the same rows together, and the visible keys cut into
     # runs (a block each, records merged by a second kernel) until the step fills the device about twice.  How many keys
     # a token can see at most is known from the window or from the step's bound on cached positions.
-    few = 1 if n * H <= 8 * 148 else 0
+    few = 1 if (batch.is_decode or n * H <= 8 * 148) else 0
     runs, partial = 1, None
     if few:
         group = 1 if maps == 2 else (4 if (H // kv_heads) % 4 == 0 else (2 if (H // kv_heads) % 2 == 0 else 1))
