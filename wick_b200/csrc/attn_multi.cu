@@ -584,11 +584,12 @@ int attn_multi(const void* q, const void* store, void* out, float* partial, cons
     if (n == 0) return 0;
     if (runs == 1) partial = nullptr;
     const int per_kv = H / G;
-    // (eight warps a block for a step of few tokens; four where the warps' results would fill a block's shared memory)
+    // (eight warps a block for a step of few tokens; four where the warps' results would fill a block's shared memory
+    // and the step has blocks enough to fill the device twice without them)
 #define WICK_AM(GROUP, CH)                                                                                                       \
     return attn_multi_launch<T, TQ, TO, MAPS, GROUP, CH>(q, store, out, partial, seq_of_token, positions, page_table, table_width, n, H, \
                                                          G, dm, e, page_elems, k_row, v_off, v_row, scale, window, keep_first, sink, \
-                                                         lam, eps, factor, few ? (GROUP * CH > 4 ? 4 : 8) : 1, runs, s)
+                                                         lam, eps, factor, few ? (GROUP * CH > 4 && (int64_t)n * (H / GROUP) * runs > 2 * sm_count() ? 4 : 8) : 1, runs, s)
     if (e <= 128) {
         if (MAPS == 1 && few && per_kv % 4 == 0) WICK_AM(4, 1);
         if (MAPS == 1 && few && per_kv % 2 == 0) WICK_AM(2, 1);
