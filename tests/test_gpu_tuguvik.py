@@ -782,6 +782,40 @@ def test_greedy_generation_through_the_library_entry(name):
             assert row[t] >= row.max() - 0.06 * max(1.0, row.abs().max().item())
 
 
+def test_the_command_line_writes_runs_and_times_the_design(tmp_path):
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=root)
+    cmd = [sys.executable, os.path.join(root, "bin", "wick")]
+    cfg_path, d = str(tmp_path / "cfg.json"), str(tmp_path / "m")
+    with open(cfg_path, "w") as f:
+        json.dump(CONFIG_TA, f)
+    r = subprocess.run(cmd + ["random", d, "--config", cfg_path, "--seed", "4"], capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stderr
+    st = SafeTensorsDir(d)
+    w = {n: st.get(n).tensor() for n in st.names()}
+    prompts = [[5, 17, 3], [9, 9, 200, 1, 77, 3, 3, 14]]
+    r = subprocess.run(cmd + ["run", d, "--ids", "5,17,3", "--ids", "9,9,200,1,77,3,3,14", "-n", "6", "-t", "0", "-q", "f32"],
+                       capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stderr
+    assert "Tuguvik" in r.stderr and "4 layers" in r.stderr
+    lines = [json.loads(l) for l in r.stdout.strip().splitlines()]
+    for p, toks in zip(prompts, lines):
+        assert len(toks) == 6
+        ref = P.forward(CONFIG_TA, w, p + toks).float()
+        for i, t in enumerate(toks):
+            row = ref[len(p) - 1 + i]
+            assert row[t] >= row.max() - 1e-3, (p, i)
+    # sampling with a temperature and a cut: the same seed gives the same tokens, all inside the vocabulary
+    args = ["run", d, "--ids", "5,17,3", "-n", "12", "-t", "0.9", "--top-k", "20", "--seed", "7", "-q", "bf16"]
+    a = subprocess.run(cmd + args, capture_output=True, text=True, env=env, timeout=600)
+    b = subprocess.run(cmd + args, capture_output=True, text=True, env=env, timeout=600)
+    assert a.returncode == 0 and a.stdout == b.stdout, a.stderr
+    assert all(0 <= t < CONFIG_TA["vocab"] for t in json.loads(a.stdout.strip().splitlines()[0]))
+    r = subprocess.run(cmd + ["bench", d, "--prompt-len", "16", "-n", "4", "--batch", "2", "-q", "bf16"],
+                       capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0 and "tok/s" in r.stdout, r.stderr
+
+
 def test_the_trace_runner_serves_the_design():
     name = "TA"
     d = model(name)[0]

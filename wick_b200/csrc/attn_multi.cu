@@ -66,6 +66,84 @@ __device__ __forceinline__ void finish_head(float (&y)[MAPS][4 * MV_CHUNKS], int
     }
 }
 
+// The end of a block's work: the warps' running maxima, sums and unnormalised results (ms, accs: shared memory) are
+// folded in warp order, head gi by warp gi; the result goes out as a record for the merge kernel (`partial`) or, where
+// the block held all visible keys, is finished here (sink, division, two maps combined).
+template <typename TO, int MAPS, int GROUP, int MV_CHUNKS>
+__device__ __forceinline__ void fold_warps(float (&m)[MAPS * GROUP], float (&l)[MAPS * GROUP], float (&acc)[MAPS * GROUP][4 * MV_CHUNKS],
+                                           float* ms, float* accs, TO* __restrict__ out, float* __restrict__ partial, int t, int h0,
+                                           int H, int e, const float* __restrict__ sink, float lam, float eps, float factor) {
+    constexpr int NQ = MAPS * GROUP;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int e_pad = (e + 127) / 128 * 128;
+    if (lane == 0) {
+#pragma unroll
+        for (int a = 0; a < NQ; ++a) {
+            ms[warp * NQ + a] = m[a];
+            ms[(n_warps + warp) * NQ + a] = l[a];
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < NQ; ++a)
+#pragma unroll
+        for (int c = 0; c < MV_CHUNKS; ++c)
+            if (128 * c < e_pad)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) accs[((int64_t)warp * NQ + a) * e_pad + 128 * c + 4 * lane + i] = acc[a][4 * c + i];
+    __syncthreads();
+    // warp gi folds head gi's maps over the block's warps; a lane holds its elements of the head's result
+    for (int gi = warp; gi < GROUP; gi += n_warps) {
+        const int h = h0 + gi;
+        float y[MAPS][4 * MV_CHUNKS];
+#pragma unroll
+        for (int a = 0; a < MAPS; ++a) {
+            const int qa = gi * MAPS + a;
+            const bool with_sink = sink && !partial;
+            float big = with_sink ? sink[h] : -INFINITY;
+            for (int w = 0; w < n_warps; ++w) big = fmaxf(big, ms[w * NQ + qa]);
+            float sum = with_sink ? expf(sink[h] - big) : 0.f;
+#pragma unroll
+            for (int c = 0; c < 4 * MV_CHUNKS; ++c) y[a][c] = 0.f;
+            for (int w = 0; w < n_warps; ++w) {
+                const float mw = ms[w * NQ + qa];
+                const float f = mw == -INFINITY ? 0.f : expf(mw - big);
+                sum += ms[(n_warps + w) * NQ + qa] * f;
+#pragma unroll
+                for (int c = 0; c < MV_CHUNKS; ++c)
+                    if (128 * c < e_pad)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            y[a][4 * c + i] = fmaf(accs[((int64_t)w * NQ + qa) * e_pad + 128 * c + 4 * lane + i], f, y[a][4 * c + i]);
+            }
+            if (partial) {                       // a record: maximum, sum, then the unnormalised values
+                float* rec = partial + ((((int64_t)t * H + h) * MAPS + a) * gridDim.y + blockIdx.y) * (4 + e_pad);
+                if (lane == 0) {
+                    rec[0] = big;
+                    rec[1] = sum;
+                }
+#pragma unroll
+                for (int c = 0; c < MV_CHUNKS; ++c)
+                    if (128 * c < e_pad) *reinterpret_cast<float4*>(rec + 4 + 128 * c + 4 * lane) =
+                        make_float4(y[a][4 * c], y[a][4 * c + 1], y[a][4 * c + 2], y[a][4 * c + 3]);
+            } else {
+                const float inv = 1.0f / sum;    // (the block holds a visible key: the sum is positive)
+#pragma unroll
+                for (int c = 0; c < 4 * MV_CHUNKS; ++c) y[a][c] *= inv;
+            }
+        }
+        if (partial) continue;
+        finish_head<MAPS, MV_CHUNKS>(y, lane, e, lam, eps, factor);
+        TO* o = out + ((int64_t)t * H + h) * e;
+#pragma unroll
+        for (int c = 0; c < MV_CHUNKS; ++c)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int x = 128 * c + 4 * lane + i;
+                if (x < e) st(o + x, y[0][4 * c + i]);
+            }
+    }
+}
+
 template <typename T, typename TQ, typename TO, int MAPS, int GROUP, int MV_CHUNKS>
 __global__ void __launch_bounds__(256)
 attn_multi_kernel(const TQ* __restrict__ q, const T* __restrict__ store, TO* __restrict__ out, float* __restrict__ partial,
@@ -200,72 +278,178 @@ attn_multi_kernel(const TQ* __restrict__ q, const T* __restrict__ store, TO* __r
             }
         }
     }
-    if (lane == 0) {
+    fold_warps<TO, MAPS, GROUP, MV_CHUNKS>(m, l, acc, ms, accs, out, partial, t, h0, H, e, sink, lam, eps, factor);
+}
+
+// The form for steps of few tokens where rows can be copied 16 bytes at a time: one block per (token, GROUP heads, run
+// of keys), as above, but the run's rows come through shared memory.  A tile of TK keys is copied there with cp.async
+// (every copy of a tile in flight at once, the next tile's while this one is worked on), and a key row is then read by a
+// WHOLE warp: lane l takes the row's 16-byte pieces l, l + 32, ... and its share of every query vector's dot product, the
+// 32 shares are added by the butterfly.  A warp takes the keys w, w + 8, ... of a tile, four at a time: their scores, one
+// step of the running maximum and sum, then their value rows (from the same tile in shared memory) into the lane's
+// elements of every vector's result.  The warps' results are folded as above.
+constexpr int TK = 32;                         // keys of a tile
+constexpr int TW = 8;                          // warps of a block
+
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <typename T, typename TQ, typename TO, int MAPS, int GROUP, int MV_CHUNKS>
+__global__ void __launch_bounds__(32 * TW)
+attn_multi_tile_kernel(const TQ* __restrict__ q, const T* __restrict__ store, TO* __restrict__ out, float* __restrict__ partial,
+                       const int* __restrict__ seq_of_token, const int* __restrict__ positions,
+                       const int* __restrict__ page_table, int table_width, int H, int G, int dm, int e, int64_t page_elems,
+                       int k_row, int64_t v_off, int v_row, float scale, int window, int keep_first,
+                       const float* __restrict__ sink, float lam, float eps, float factor) {
+    constexpr int NQ = MAPS * GROUP;
+    constexpr int VN = Vec16<T>::N;
+    extern __shared__ __align__(16) float smem[];
+    pdl_trigger();
+    pdl_wait();
+    q = fresh(q);
+    store = fresh(store);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int groups = H / GROUP;
+    const int t = blockIdx.x / groups, h0 = (blockIdx.x - t * groups) * GROUP;
+    const int g = h0 / (H / G);
+    const int pos = positions[t];
+    const int* table = page_table + (int64_t)seq_of_token[t] * table_width;
+    const int kd = MAPS * dm;                   // numbers of a key row
+    const bool v_same = v_off == 0 && v_row == k_row;          // the value is the first e numbers of the key row
+    const int row_elems = kd + (v_same ? 0 : e);                // a key's numbers in a tile: its key row, then its value row
+    const int dq = NQ * dm, dq_pad = (dq + 3) & ~3, e_pad = (e + 127) / 128 * 128;
+    float* qs = smem;                           // [NQ][dm]
+    float* ms = qs + dq_pad;                    // [warps][NQ] maxima, then [warps][NQ] sums
+    T* tiles = reinterpret_cast<T*>(ms + ((2 * NQ * TW + 3) & ~3));   // [2][TK][row_elems]; afterwards the warps' results
+    float* accs = reinterpret_cast<float*>(tiles);
+    for (int x = tid; x < dq; x += blockDim.x) qs[x] = ld(q + ((int64_t)t * H + h0) * (MAPS * dm) + x);
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int n_kept = window > 0 ? min(keep_first, lo) : 0;
+    const int total = n_kept + (pos - lo + 1);
+    const int n_tiles_all = (total + TK - 1) / TK, per_run = (n_tiles_all + (int)gridDim.y - 1) / (int)gridDim.y;
+    const int v_begin = TK * per_run * (int)blockIdx.y, v_end = min(total, TK * per_run * ((int)blockIdx.y + 1));
+    const int n_tiles = v_end > v_begin ? (v_end - v_begin + TK - 1) / TK : 0;
+    const int kch = kd / VN, vch = v_same ? 0 : e / VN, rch = kch + vch;      // 16-byte pieces of a key's rows
+
+    auto load_tile = [&](int it) {
+        T* dst = tiles + (int64_t)(it & 1) * TK * row_elems;
+        const int v0 = v_begin + it * TK, n_keys = min(TK, v_end - v0);
+        for (int x = tid; x < n_keys * rch; x += blockDim.x) {
+            const int kk = x / rch, c = x - kk * rch;
+            const int key = visible_key(v0 + kk, n_kept, lo);
+            const int64_t in_page = (int64_t)table[key / kPage] * page_elems, place = (int64_t)g * kPage + (key % kPage);
+            const T* src = c < kch ? store + in_page + place * k_row + c * VN : store + in_page + v_off + place * v_row + (c - kch) * VN;
+            cp_async_16(dst + (int64_t)kk * row_elems + c * VN, src);
+        }
+    };
+    if (n_tiles > 0) load_tile(0);
+    cp_async_commit_group();
+
+    float m[NQ], l[NQ], acc[NQ][4 * MV_CHUNKS];
+#pragma unroll
+    for (int a = 0; a < NQ; ++a) {
+        m[a] = -INFINITY;
+        l[a] = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4 * MV_CHUNKS; ++c) acc[a][c] = 0.f;
+    }
+    constexpr int KW = TK / TW;                 // keys of a tile that one warp takes
+    for (int it = 0; it < n_tiles; ++it) {
+        if (it + 1 < n_tiles) {
+            load_tile(it + 1);
+            cp_async_commit_group();
+            cp_async_wait_group<1>();
+        } else {
+            cp_async_wait_group<0>();
+        }
+        __syncthreads();
+        const T* tile = tiles + (int64_t)(it & 1) * TK * row_elems;
+        const int n_keys = min(TK, v_end - (v_begin + it * TK));
+        // scores of this warp's keys: a lane's share of every dot product, then the butterfly
+        float s[KW][NQ];
+#pragma unroll
+        for (int j = 0; j < KW; ++j) {
+            const int kk = warp + TW * j;
+#pragma unroll
+            for (int a = 0; a < NQ; ++a) s[j][a] = 0.f;
+            if (kk < n_keys) {
+                const T* kr = tile + (int64_t)kk * row_elems;
+                for (int c = lane; c < kch; c += 32) {
+                    Vec16<T> kv;
+                    kv.load(kr + c * VN);
+                    const int x0 = c * VN, a_of = MAPS == 1 ? 0 : x0 / dm, x_in = x0 - a_of * dm;
+#pragma unroll
+                    for (int gi = 0; gi < GROUP; ++gi)
+#pragma unroll
+                        for (int a = 0; a < MAPS; ++a) {
+                            if (MAPS > 1 && a != a_of) continue;
+                            const float* qa = qs + (gi * MAPS + a) * dm + x_in;
+                            float dot = s[j][gi * MAPS + a];
+#pragma unroll
+                            for (int i = 0; i < VN; i += 4) {
+                                const float4 q4 = *reinterpret_cast<const float4*>(qa + i);
+                                dot = fmaf(q4.x, kv.v[i], dot);
+                                dot = fmaf(q4.y, kv.v[i + 1], dot);
+                                dot = fmaf(q4.z, kv.v[i + 2], dot);
+                                dot = fmaf(q4.w, kv.v[i + 3], dot);
+                            }
+                            s[j][gi * MAPS + a] = dot;
+                        }
+                }
+            }
+#pragma unroll
+            for (int a = 0; a < NQ; ++a) s[j][a] = kk < n_keys ? warp_sum(s[j][a]) * scale : -INFINITY;
+        }
+        // one step of the running maximum and sum for the warp's keys of this tile
+        float p[KW][NQ];
 #pragma unroll
         for (int a = 0; a < NQ; ++a) {
-            ms[warp * NQ + a] = m[a];
-            ms[(n_warps + warp) * NQ + a] = l[a];
-        }
-    }
+            float mx = m[a];
 #pragma unroll
-    for (int a = 0; a < NQ; ++a)
+            for (int j = 0; j < KW; ++j) mx = fmaxf(mx, s[j][a]);
+            if (mx == -INFINITY) {              // (the warp has seen no key yet)
 #pragma unroll
-        for (int c = 0; c < MV_CHUNKS; ++c)
-            if (128 * c < e_pad)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) accs[((int64_t)warp * NQ + a) * e_pad + 128 * c + 4 * lane + i] = acc[a][4 * c + i];
-    __syncthreads();
-    // warp gi folds head gi's maps over the block's warps; a lane holds its elements of the head's result
-    for (int gi = warp; gi < GROUP; gi += n_warps) {
-        const int h = h0 + gi;
-        float y[MAPS][4 * MV_CHUNKS];
-#pragma unroll
-        for (int a = 0; a < MAPS; ++a) {
-            const int qa = gi * MAPS + a;
-            const bool with_sink = sink && !partial;
-            float big = with_sink ? sink[h] : -INFINITY;
-            for (int w = 0; w < n_warps; ++w) big = fmaxf(big, ms[w * NQ + qa]);
-            float sum = with_sink ? expf(sink[h] - big) : 0.f;
-#pragma unroll
-            for (int c = 0; c < 4 * MV_CHUNKS; ++c) y[a][c] = 0.f;
-            for (int w = 0; w < n_warps; ++w) {
-                const float mw = ms[w * NQ + qa];
-                const float f = mw == -INFINITY ? 0.f : expf(mw - big);
-                sum += ms[(n_warps + w) * NQ + qa] * f;
-#pragma unroll
-                for (int c = 0; c < MV_CHUNKS; ++c)
-                    if (128 * c < e_pad)
-#pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            y[a][4 * c + i] = fmaf(accs[((int64_t)w * NQ + qa) * e_pad + 128 * c + 4 * lane + i], f, y[a][4 * c + i]);
+                for (int j = 0; j < KW; ++j) p[j][a] = 0.f;
+                continue;
             }
-            if (partial) {                       // a record: maximum, sum, then the unnormalised values
-                float* rec = partial + ((((int64_t)t * H + h) * MAPS + a) * gridDim.y + blockIdx.y) * (4 + e_pad);
-                if (lane == 0) {
-                    rec[0] = big;
-                    rec[1] = sum;
+            const float corr = expf(m[a] - mx);
+            float sum = 0.f;
+#pragma unroll
+            for (int j = 0; j < KW; ++j) {
+                p[j][a] = expf(s[j][a] - mx);   // (a key beyond the run's end: exp(-inf) = 0)
+                sum += p[j][a];
+            }
+            l[a] = l[a] * corr + sum;
+            m[a] = mx;
+#pragma unroll
+            for (int c = 0; c < 4 * MV_CHUNKS; ++c) acc[a][c] *= corr;
+        }
+        // the keys' value rows, from the tile
+#pragma unroll
+        for (int j = 0; j < KW; ++j) {
+            const int kk = warp + TW * j;
+            if (kk >= n_keys) continue;
+            const T* vr = tile + (int64_t)kk * row_elems + (v_same ? 0 : kd);
+#pragma unroll
+            for (int c = 0; c < MV_CHUNKS; ++c) {
+                const int x = 128 * c + 4 * lane;
+                if (x < e) {
+                    float vv[4];
+                    mv_load4(vr + x, vv);
+#pragma unroll
+                    for (int a = 0; a < NQ; ++a)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) acc[a][4 * c + i] = fmaf(p[j][a], vv[i], acc[a][4 * c + i]);
                 }
-#pragma unroll
-                for (int c = 0; c < MV_CHUNKS; ++c)
-                    if (128 * c < e_pad) *reinterpret_cast<float4*>(rec + 4 + 128 * c + 4 * lane) =
-                        make_float4(y[a][4 * c], y[a][4 * c + 1], y[a][4 * c + 2], y[a][4 * c + 3]);
-            } else {
-                const float inv = 1.0f / sum;    // (the block holds a visible key: the sum is positive)
-#pragma unroll
-                for (int c = 0; c < 4 * MV_CHUNKS; ++c) y[a][c] *= inv;
             }
         }
-        if (partial) continue;
-        finish_head<MAPS, MV_CHUNKS>(y, lane, e, lam, eps, factor);
-        TO* o = out + ((int64_t)t * H + h) * e;
-#pragma unroll
-        for (int c = 0; c < MV_CHUNKS; ++c)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int x = 128 * c + 4 * lane + i;
-                if (x < e) st(o + x, y[0][4 * c + i]);
-            }
+        __syncthreads();                        // everyone is done with this buffer
     }
+    fold_warps<TO, MAPS, GROUP, MV_CHUNKS>(m, l, acc, ms, accs, out, partial, t, h0, H, e, sink, lam, eps, factor);
 }
 
 // One warp per (token, head): the records of the runs of keys (a run that held no key has the maximum -inf) are
@@ -548,7 +732,35 @@ int attn_multi_launch(const void* q, const void* store, void* out, float* partia
                       int64_t v_off, int v_row, float scale, int window, int keep_first, const float* sink, float lam, float eps,
                       float factor, int warps, int runs, cudaStream_t s) {
     constexpr int NQ = MAPS * GROUP;
+    constexpr int VN = Vec16<T>::N;
     const int dq_pad = (NQ * dm + 3) & ~3, e_pad = (e + 127) / 128 * 128;
+    // rows that can be copied 16 bytes at a time, in a step of few tokens: the form that reads them through shared memory
+    const bool v_same = v_off == 0 && v_row == k_row;
+    const bool copies = warps > 1 && ((uintptr_t)store & 15) == 0 && dm % VN == 0 && k_row % VN == 0 && page_elems % VN == 0 &&
+                        e % VN == 0 && v_row % VN == 0 && v_off % VN == 0 && e % 4 == 0 && (MAPS * dm == k_row || !v_same);
+    if (copies) {
+        const size_t row_elems = (size_t)MAPS * dm + (v_same ? 0 : e);
+        const size_t tile_bytes = 2 * TK * row_elems * sizeof(T), fold_bytes = (size_t)TW * NQ * e_pad * sizeof(float);
+        const size_t smem = ((size_t)dq_pad + ((2 * NQ * TW + 3) & ~3)) * sizeof(float) + (tile_bytes > fold_bytes ? tile_bytes : fold_bytes);
+        if (smem <= 200 * 1024) {
+            static size_t raised = 48 * 1024;
+            if (smem > raised) {
+                WICK_CUDA(cudaFuncSetAttribute(attn_multi_tile_kernel<T, TQ, TO, MAPS, GROUP, MV_CHUNKS>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+                raised = 200 * 1024;
+            }
+            WICK_CUDA(launch(attn_multi_tile_kernel<T, TQ, TO, MAPS, GROUP, MV_CHUNKS>, dim3((unsigned)(n * (H / GROUP)), runs), dim3(32 * TW),
+                             smem, s, (const TQ*)q, (const T*)store, (TO*)out, partial, seq_of_token, positions, page_table, table_width,
+                             H, G, dm, e, page_elems, k_row, v_off, v_row, scale, window, keep_first, sink, lam, eps, factor));
+            if (int rc = check_launch("attn_multi_tile")) return rc;
+            if (partial) {
+                WICK_CUDA(launch(attn_multi_merge_kernel<TO, MAPS, MV_CHUNKS>, dim3(ceil_div((int64_t)n * H, 4)), dim3(128), 0, s,
+                                 (const float*)partial, (TO*)out, n * H, H, e, runs, sink, lam, eps, factor));
+                return check_launch("attn_multi_merge");
+            }
+            return 0;
+        }
+    }
     const size_t smem = ((size_t)dq_pad + 2 * NQ * warps + (size_t)warps * NQ * e_pad) * sizeof(float);
     WICK_REQUIRE(smem <= 160 * 1024, "attn_multi: heads of %d numbers are beyond one block's shared memory", NQ * dm);
     static size_t raised = 48 * 1024;

@@ -701,7 +701,7 @@ def attention_multi(q: torch.Tensor, store: torch.Tensor, batch, scale: float, *
         bound = getattr(batch, "kv_bound", None) or batch.max_kv_len
         keys = min(bound, window + keep_first) if window > 0 else bound
         tiles = (max(1, keys) + 31) // 32
-        runs = max(1, min(-(-2 * 148 // (n * (H // group))), tiles // 8, 16))
+        runs = max(1, min(-(-2 * 148 // (n * (H // group))), tiles // 2, 16))        # (a run is two tiles of 32 keys at least)
         if runs > 1:
             need = n * H * maps * runs * (4 + (v_dim + 127) // 128 * 128)
             ws = getattr(batch, "workspace", None)
