@@ -290,6 +290,7 @@ attn_multi_kernel(const TQ* __restrict__ q, const T* __restrict__ store, TO* __r
 // elements of every vector's result.  The warps' results are folded as above.
 constexpr int TK = 32;                         // keys of a tile
 constexpr int TW = 8;                          // warps of a block
+constexpr int TS = 2;                          // tiles in shared memory: one worked on, one on its way (three were measured: slower, fewer blocks fit an SM)
 
 __device__ __forceinline__ void cp_async_16(void* dst, const void* src) {
     const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
@@ -324,7 +325,7 @@ attn_multi_tile_kernel(const TQ* __restrict__ q, const T* __restrict__ store, TO
     const int dq = NQ * dm, dq_pad = (dq + 3) & ~3, e_pad = (e + 127) / 128 * 128;
     float* qs = smem;                           // [NQ][dm]
     float* ms = qs + dq_pad;                    // [warps][NQ] maxima, then [warps][NQ] sums
-    T* tiles = reinterpret_cast<T*>(ms + ((2 * NQ * TW + 3) & ~3));   // [2][TK][row_elems]; afterwards the warps' results
+    T* tiles = reinterpret_cast<T*>(ms + ((2 * NQ * TW + 3) & ~3));   // [TS][TK][row_elems]; afterwards the warps' results
     float* accs = reinterpret_cast<float*>(tiles);
     for (int x = tid; x < dq; x += blockDim.x) qs[x] = ld(q + ((int64_t)t * H + h0) * (MAPS * dm) + x);
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
@@ -336,7 +337,7 @@ attn_multi_tile_kernel(const TQ* __restrict__ q, const T* __restrict__ store, TO
     const int kch = kd / VN, vch = v_same ? 0 : e / VN, rch = kch + vch;      // 16-byte pieces of a key's rows
 
     auto load_tile = [&](int it) {
-        T* dst = tiles + (int64_t)(it & 1) * TK * row_elems;
+        T* dst = tiles + (int64_t)(it % TS) * TK * row_elems;
         const int v0 = v_begin + it * TK, n_keys = min(TK, v_end - v0);
         for (int x = tid; x < n_keys * rch; x += blockDim.x) {
             const int kk = x / rch, c = x - kk * rch;
@@ -346,8 +347,11 @@ attn_multi_tile_kernel(const TQ* __restrict__ q, const T* __restrict__ store, TO
             cp_async_16(dst + (int64_t)kk * row_elems + c * VN, src);
         }
     };
-    if (n_tiles > 0) load_tile(0);
-    cp_async_commit_group();
+#pragma unroll
+    for (int it = 0; it < TS - 1; ++it) {       // (a group per tile, empty beyond the last, so that the waits below count alike)
+        if (it < n_tiles) load_tile(it);
+        cp_async_commit_group();
+    }
 
     float m[NQ], l[NQ], acc[NQ][4 * MV_CHUNKS];
 #pragma unroll
@@ -359,15 +363,11 @@ attn_multi_tile_kernel(const TQ* __restrict__ q, const T* __restrict__ store, TO
     }
     constexpr int KW = TK / TW;                 // keys of a tile that one warp takes
     for (int it = 0; it < n_tiles; ++it) {
-        if (it + 1 < n_tiles) {
-            load_tile(it + 1);
-            cp_async_commit_group();
-            cp_async_wait_group<1>();
-        } else {
-            cp_async_wait_group<0>();
-        }
+        if (it + TS - 1 < n_tiles) load_tile(it + TS - 1);       // (into the buffer that the barrier at the end of the last round freed)
+        cp_async_commit_group();
+        cp_async_wait_group<TS - 1>();
         __syncthreads();
-        const T* tile = tiles + (int64_t)(it & 1) * TK * row_elems;
+        const T* tile = tiles + (int64_t)(it % TS) * TK * row_elems;
         const int n_keys = min(TK, v_end - (v_begin + it * TK));
         // scores of this warp's keys: a lane's share of every dot product, then the butterfly
         float s[KW][NQ];
@@ -740,7 +740,7 @@ int attn_multi_launch(const void* q, const void* store, void* out, float* partia
                         e % VN == 0 && v_row % VN == 0 && v_off % VN == 0 && e % 4 == 0 && (MAPS * dm == k_row || !v_same);
     if (copies) {
         const size_t row_elems = (size_t)MAPS * dm + (v_same ? 0 : e);
-        const size_t tile_bytes = 2 * TK * row_elems * sizeof(T), fold_bytes = (size_t)TW * NQ * e_pad * sizeof(float);
+        const size_t tile_bytes = (size_t)TS * TK * row_elems * sizeof(T), fold_bytes = (size_t)TW * NQ * e_pad * sizeof(float);
         const size_t smem = ((size_t)dq_pad + ((2 * NQ * TW + 3) & ~3)) * sizeof(float) + (tile_bytes > fold_bytes ? tile_bytes : fold_bytes);
         if (smem <= 200 * 1024) {
             static size_t raised = 48 * 1024;
