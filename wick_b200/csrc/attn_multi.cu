@@ -1,7 +1,8 @@
 // Attention whose heads hold more than one score map, over paged storage described by
 // strides, and the kernels around attention through a cached latent.
 //
-//   attend   : every new token over the cache (for steps of few tokens: the keys in runs over several blocks, then a merge).  A query head holds MAPS vectors of dm numbers;
+//   attend   : every new token over the cache (steps of few tokens: rows through shared memory, the keys in runs
+//              over several blocks, then a merge).  A query head holds MAPS vectors of dm numbers;
 //              map a scores the a-th dm numbers of the key row, has a softmax of its own, and
 //              weighs the SAME value rows.  Visible keys of the query at position p: with a
 //              window, the keys j <= p with p - j < window or j < keep_first; else every j <= p.
