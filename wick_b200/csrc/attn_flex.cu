@@ -28,6 +28,9 @@ constexpr int KCH = DK / 8, VCH = DV / 8;            // 16-byte chunks per row
 constexpr bool KSWZ = KCH % 8 == 0, VSWZ = VCH % 8 == 0;
 constexpr int KS = DK / 16;                          // k-steps of Q K^T
 constexpr int ND = DV / 8;                           // 8-wide blocks of the output row
+// Blocks an SM should hold: three where a thread's accumulators are few enough for 170 registers (8 warps an SM leave the
+// tensor pipe waiting on every instruction's latency; measured 28 % active), two for the large sizes.
+constexpr int MIN_BLOCKS = DK + DV <= 192 ? 3 : 2;
 typedef __nv_bfloat16 bf16;
 
 __device__ __forceinline__ int kswz(int row, int chunk) { return KSWZ ? (chunk ^ (row & 7)) : chunk; }
@@ -89,7 +92,7 @@ struct Params {
     float scale;
 };
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, MIN_BLOCKS)
 attn_flex_kernel(const Params P) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);              // [64][DK]
