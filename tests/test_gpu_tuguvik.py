@@ -121,7 +121,6 @@ def close(got, ref, dtype, what="", tol=None):
 
 
 DTYPES = ["float32", "bfloat16"]
-TORCH = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 
 
 def seq_batch(n_new, start=0, pages=None):
@@ -526,9 +525,7 @@ def test_keys_of_two_parts_from_the_steps_own_rows(H, d, dr, e, window):
     kr = torch.randn(n, dr, generator=g).to(torch.bfloat16)
     sink, gate = torch.randn(H, generator=g), torch.rand(n, H, generator=g)
     b = ragged_batch(lens, [0, 0], [[1, 2, 3], [4, 5, 6, 7]])
-    k0 = ops.flex_source(kvx.to(DEV), hmul=d, row_stride=H * (d + e), length=d)
-    kvd = kvx.to(DEV)
-    krd = kr.to(DEV)
+    kvd, krd = kvx.to(DEV), kr.to(DEV)
     k0 = ops.flex_source(kvd, hmul=d, row_stride=H * (d + e), length=d)
     out = ops.attention_flex(q.to(DEV), k0, ops.flex_source(krd, row_stride=dr, length=dr),
                              ops.flex_source(kvd, const_off=H * d, hmul=e, row_stride=H * (d + e), length=e), b, 0.1, dv=e,
