@@ -671,7 +671,8 @@ latent_absorb_kernel(const float* __restrict__ parts, int splits, int64_t split_
         float acc[LAT_TT];
 #pragma unroll
         for (int tt = 0; tt < LAT_TT; ++tt) acc[tt] = 0.f;
-        for (int x = 0; x < d; ++x) {
+#pragma unroll 8
+        for (int x = 0; x < d; ++x) {                 // (eight rows' loads in flight: the kernel waits for them, not for arithmetic)
             const float wv = ld(w + (int64_t)x * r + j);
             const float4 qa = *reinterpret_cast<const float4*>(qh + x * LAT_TT), qb = *reinterpret_cast<const float4*>(qh + x * LAT_TT + 4);
             acc[0] = fmaf(qa.x, wv, acc[0]); acc[1] = fmaf(qa.y, wv, acc[1]); acc[2] = fmaf(qa.z, wv, acc[2]); acc[3] = fmaf(qa.w, wv, acc[3]);
@@ -707,6 +708,7 @@ latent_expand_kernel(const float* __restrict__ y, const T* __restrict__ uv, cons
         float acc[LAT_TT];
 #pragma unroll
         for (int tt = 0; tt < LAT_TT; ++tt) acc[tt] = 0.f;
+#pragma unroll 4
         for (int j = lane; j < r; j += 32) {
             const float wv = ld(w + j);
             const float4 ya = *reinterpret_cast<const float4*>(ys + j * LAT_TT), yb = *reinterpret_cast<const float4*>(ys + j * LAT_TT + 4);
