@@ -335,17 +335,23 @@ attn_multi_tile_kernel(const TQ* __restrict__ q, const T* __restrict__ store, TO
     const int n_tiles_all = (total + TK - 1) / TK, per_run = (n_tiles_all + (int)gridDim.y - 1) / (int)gridDim.y;
     const int v_begin = TK * per_run * (int)blockIdx.y, v_end = min(total, TK * per_run * ((int)blockIdx.y + 1));
     const int n_tiles = v_end > v_begin ? (v_end - v_begin + TK - 1) / TK : 0;
-    const int kch = kd / VN, vch = v_same ? 0 : e / VN, rch = kch + vch;      // 16-byte pieces of a key's rows
+    const int kch = kd / VN, vch = v_same ? 0 : e / VN;                       // 16-byte pieces of a key's two rows
 
+    // A key's rows are copied by 256 / TK neighbouring threads, which work out where the rows lie once a tile (the place of
+    // every 16-byte piece on its own cost more instructions than the arithmetic on the tile).
     auto load_tile = [&](int it) {
+        constexpr int TPK = 32 * TW / TK;       // threads that share a key
         T* dst = tiles + (int64_t)(it % TS) * TK * row_elems;
         const int v0 = v_begin + it * TK, n_keys = min(TK, v_end - v0);
-        for (int x = tid; x < n_keys * rch; x += blockDim.x) {
-            const int kk = x / rch, c = x - kk * rch;
+        const int kk = tid / TPK, c0 = tid % TPK;
+        if (kk < n_keys) {
             const int key = visible_key(v0 + kk, n_kept, lo);
             const int64_t in_page = (int64_t)table[key / kPage] * page_elems, place = (int64_t)g * kPage + (key % kPage);
-            const T* src = c < kch ? store + in_page + place * k_row + c * VN : store + in_page + v_off + place * v_row + (c - kch) * VN;
-            cp_async_16(dst + (int64_t)kk * row_elems + c * VN, src);
+            const T* ksrc = store + in_page + place * k_row;
+            const T* vsrc = store + in_page + v_off + place * v_row;
+            T* d = dst + (int64_t)kk * row_elems;
+            for (int c = c0; c < kch; c += TPK) cp_async_16(d + c * VN, ksrc + c * VN);
+            for (int c = c0; c < vch; c += TPK) cp_async_16(d + kd + c * VN, vsrc + c * VN);
         }
     };
 #pragma unroll
